@@ -1,0 +1,44 @@
+#pragma once
+// Entry points the JIT-generated `launch` bodies call for the attention forward path.
+// Replaces fray::flash_attn_cute<R,C,D> (fray/include/flash_attn/flashattn_cute.cuh:166-239):
+// same fp16 [B,H,S,D] operands and in-place output, plus explicit strides, an optional
+// causal mask and an explicit softmax scale.
+
+#include "fwd_simple_sm100.cuh"
+#include "host_sm100.cuh"
+#if __has_include("fwd_ws_sm100.cuh")
+#include "fwd_ws_sm100.cuh"
+#define FRAY_HAS_WS_KERNEL 1
+#endif
+
+namespace fray {
+
+// Kernel families selectable from the tuning space.
+enum AttnKernelKind : int {
+  kAttnSimple = 0,  // one 128-row tile per CTA, single role, no overlap
+  kAttnWarpSpecialized = 1,  // two 128-row tiles per CTA, producer / MMA / softmax / correction roles
+};
+
+// KIND, D, BLOCK_N, STAGES are compile-time tuning keys; everything else is a run-time
+// argument. `rc` receives an AttnReturnCode; a non-zero value means nothing was launched.
+template <int KIND, int D, int BLOCK_N, int STAGES>
+inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, __half* o, int batch_size,
+                             int num_heads, int seq_len, int q_sb, int q_sh, int q_ss, int k_sb, int k_sh, int k_ss,
+                             int v_sb, int v_sh, int v_ss, int o_sb, int o_sh, int o_ss, bool causal, float scale,
+                             cudaStream_t stream, int& rc) {
+  const AttnShape shp{batch_size, num_heads, seq_len, D};
+  const AttnStrides st[4] = {{q_sb, q_sh, q_ss}, {k_sb, k_sh, k_ss}, {v_sb, v_sh, v_ss}, {o_sb, o_sh, o_ss}};
+  rc = validate_attn_args(q, k, v, o, shp, st);
+  if (rc != kAttnOk) return;
+  if constexpr (KIND == kAttnSimple) {
+    rc = sm100::launch_attn_fwd_simple<D, BLOCK_N>(q, k, v, o, shp, st, causal, scale, stream);
+  } else {
+#ifdef FRAY_HAS_WS_KERNEL
+    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES>(q, k, v, o, shp, st, causal, scale, stream);
+#else
+    static_assert(KIND == kAttnSimple, "warp-specialised kernel not available in this build");
+#endif
+  }
+}
+
+}  // namespace fray

@@ -1,0 +1,106 @@
+#pragma once
+// Host-side helpers shared by the sm_100a attention launchers: argument validation,
+// return codes, TMA tensor-map construction (driver entry point resolved at run time so
+// the generated library needs no link-time libcuda) and device status readback.
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sm100_ptx.cuh"
+
+namespace fray {
+
+// Values written to `__return_code` by the launchers. 0 means the kernel was queued.
+enum AttnReturnCode : int {
+  kAttnOk = 0,
+  kAttnBadShape = 1,        // batch/heads/seq_len not positive, or seq_len too large
+  kAttnBadPointer = 2,      // null or not 16-byte aligned
+  kAttnBadStride = 3,       // a stride is not a positive multiple of 8 elements (16 bytes)
+  kAttnNoDriverEntry = 5,   // cuTensorMapEncodeTiled could not be resolved
+  kAttnTensorMapFailed = 6, // the driver rejected the tensor map (layout not expressible)
+  kAttnSmemAttrFailed = 7,  // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed
+  kAttnLaunchFailed = 8,    // the launch itself reported an error
+};
+
+// Element strides of one [B,H,S,D] tensor; the D stride is 1 by contract.
+struct AttnStrides {
+  int64_t b, h, s;
+};
+
+struct AttnShape {
+  int B, H, S, D;
+};
+
+inline int validate_attn_args(const void* q, const void* k, const void* v, const void* o, const AttnShape& shp,
+                              const AttnStrides (&st)[4]) {
+  if (shp.B <= 0 || shp.H <= 0 || shp.S <= 0) return kAttnBadShape;
+  if (static_cast<int64_t>(shp.B) * shp.H > 0x7FFFFFFFLL / 2) return kAttnBadShape;
+  const void* ptrs[4] = {q, k, v, o};
+  for (int i = 0; i < 4; ++i) {
+    if (ptrs[i] == nullptr || (reinterpret_cast<uintptr_t>(ptrs[i]) & 15u) != 0) return kAttnBadPointer;
+    const int64_t s3[3] = {st[i].b, st[i].h, st[i].s};
+    const int extent[3] = {shp.B, shp.H, shp.S};
+    for (int d = 0; d < 3; ++d) {
+      if (extent[d] > 1 && (s3[d] <= 0 || (s3[d] & 7) != 0)) return kAttnBadStride;
+    }
+  }
+  return kAttnOk;
+}
+
+using PFN_encodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline PFN_encodeTiled get_encode_tiled() {
+  static PFN_encodeTiled fn = []() -> PFN_encodeTiled {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    return reinterpret_cast<PFN_encodeTiled>(p);
+  }();
+  return fn;
+}
+
+// Tensor map over an fp16 [B,H,S,D] tensor (D contiguous) whose box is
+// `box_rows` sequence positions x 64 head-dim elements (one 128-byte swizzle span).
+inline int make_attn_tensor_map(CUtensorMap* map, const void* base, const AttnShape& shp, const AttnStrides& st,
+                                int box_rows) {
+  PFN_encodeTiled enc = get_encode_tiled();
+  if (enc == nullptr) return kAttnNoDriverEntry;
+  // A size-1 mode never advances, so any legal (16-byte multiple) stride will do.
+  const int64_t sb = shp.B > 1 ? st.b : static_cast<int64_t>(shp.D);
+  const int64_t sh = shp.H > 1 ? st.h : static_cast<int64_t>(shp.D);
+  const int64_t ss = shp.S > 1 ? st.s : static_cast<int64_t>(shp.D);
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(shp.D), static_cast<cuuint64_t>(shp.S),
+                        static_cast<cuuint64_t>(shp.H), static_cast<cuuint64_t>(shp.B)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(ss) * 2, static_cast<cuuint64_t>(sh) * 2,
+                           static_cast<cuuint64_t>(sb) * 2};
+  cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(box_rows), 1u, 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? kAttnOk : kAttnTensorMapFailed;
+}
+
+// Synchronising read of the sticky device status words; clears them when asked.
+inline int read_attn_status(int* out4, bool clear) {
+  int host[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyFromSymbol(host, sm100::fray_attn_status, sizeof(host));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  for (int i = 0; i < 4; ++i) out4[i] = host[i];
+  if (clear && host[0] != 0) {
+    int zero[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(sm100::fray_attn_status, zero, sizeof(zero));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  return 0;
+}
+
+}  // namespace fray

@@ -1,0 +1,171 @@
+"""``flash_attn_cute(Q, K, V, Output)`` - fp16 attention forward written in place.
+
+Drop-in for the reference op (fray/jit_kernels/flashattn_cute.py:15-45): four fp16 CUDA
+tensors of identical shape ``[B, H, S, D]``, result stored into ``Output``, launch on
+the current stream, nothing returned.  The 4-positional call behaves as in the
+reference (non-causal, scale ``1/sqrt(D)``); ``causal`` and ``scale`` are keyword-only
+extensions.  Unlike the reference, strided views whose last dimension is contiguous are
+consumed and produced through their strides (no hidden copies, and a non-contiguous
+``Output`` really receives the result).
+"""
+import math
+import os
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+
+from .tuner import jit_tuner
+
+includes = ('"flash_attn/flash_attn_sm100.cuh"',)
+
+template = """
+// Templated args from Python JIT call
+fray::flash_attn_sm100<{KIND}, {D}, {BLOCK_N}, {STAGES}>(
+    Q, K, V, O, batch_size, num_heads, seq_len,
+    q_stride_b, q_stride_h, q_stride_s, k_stride_b, k_stride_h, k_stride_s,
+    v_stride_b, v_stride_h, v_stride_s, o_stride_b, o_stride_h, o_stride_s,
+    causal, scale, stream, __return_code);
+"""
+
+# Exported next to `launch`: blocking read (and optional clear) of the device status words.
+epilogue = """
+extern "C" EXPORT_API int fray_attn_status(int* out4, int clear) {
+    return fray::read_attn_status(out4, clear != 0);
+}
+extern "C" EXPORT_API void fray_attn_kernel_info(int* out4) {
+    out4[0] = {KIND}; out4[1] = {D}; out4[2] = {BLOCK_N}; out4[3] = {STAGES};
+}
+"""
+
+_STRIDE_NAMES = tuple(f"{t}_stride_{d}" for t in "qkvo" for d in "bhs")
+
+arg_defs = (
+    ("Q", torch.half), ("K", torch.half), ("V", torch.half), ("O", torch.half),
+    ("batch_size", int), ("num_heads", int), ("seq_len", int),
+    *((n, int) for n in _STRIDE_NAMES),
+    ("causal", bool), ("scale", float), ("stream", torch.cuda.Stream),
+)
+
+SUPPORTED_HEAD_DIMS = (64, 128)
+
+# Return codes of `launch` (flash_attn/host_sm100.cuh).
+_RC_TEXT = {
+    1: "bad shape", 2: "null or misaligned pointer", 3: "unsupported stride",
+    5: "cuTensorMapEncodeTiled not resolvable", 6: "tensor map rejected by the driver",
+    7: "could not raise the dynamic shared memory limit", 8: "kernel launch failed",
+}
+_RC_TENSOR_MAP = 6
+
+
+def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
+    """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised), KV tile, KV stages."""
+    space = [
+        {"KIND": 0, "BLOCK_N": 128, "STAGES": 1},
+        {"KIND": 0, "BLOCK_N": 64, "STAGES": 1},
+    ]
+    forced = os.getenv("FRAY_ATTN_FORCE")  # e.g. "KIND=0,BLOCK_N=64,STAGES=1"
+    if forced:
+        point = {kv.split("=")[0].strip(): int(kv.split("=")[1]) for kv in forced.split(",")}
+        return (point,)
+    return tuple(space)
+
+
+def _seq_class(seq_len: int, units: int) -> str:
+    """Coarse workload class the tuner memoises on: sequence bucket and whether the grid fills the GPU."""
+    s_bucket = 1 << max(7, (max(seq_len, 1) - 1).bit_length())
+    return f"S{min(s_bucket, 16384)}_{'big' if units * seq_len >= 148 * 256 else 'small'}"
+
+
+def _usable_strides(t: torch.Tensor) -> bool:
+    if t.stride(-1) != 1 and t.shape[-1] > 1:
+        return False
+    if t.data_ptr() % 16 != 0:
+        return False
+    return all(t.shape[i] == 1 or (t.stride(i) > 0 and t.stride(i) % 8 == 0 and t.stride(i) < 2 ** 31)
+               for i in range(3))
+
+
+def prebuild(head_dims=SUPPORTED_HEAD_DIMS) -> int:
+    """Compile every point of the tuning space ahead of time; returns how many kernels exist afterwards."""
+    from ..jit import build, cpp_format, generate
+    count = 0
+    for d in head_dims:
+        for point in tuning_space(d):
+            keys = {"D": d, **point}
+            code = generate(includes, arg_defs, cpp_format(template, keys), cpp_format(epilogue, keys))
+            build("flash_attn_cute", arg_defs, code)
+            count += 1
+    return count
+
+
+_last_runtime = None
+
+
+def flash_attn_status(clear: bool = True) -> Tuple[int, int, int, int]:
+    """Synchronise and return the device status words of the most recently used kernel library.
+
+    ``(0, 0, 0, 0)`` means healthy.  A non-zero first word is the code of the first wait
+    that ran out inside a kernel; the other words are the block indices and an iteration
+    number.  The status is sticky: until cleared, later launches of that library return
+    immediately without computing.
+    """
+    import ctypes
+    if _last_runtime is None:
+        return (0, 0, 0, 0)
+    fn = _last_runtime.symbol("fray_attn_status")
+    assert fn is not None, "kernel library does not export fray_attn_status"
+    out = (ctypes.c_int * 4)()
+    err = fn(out, ctypes.c_int(1 if clear else 0))
+    if err != 0:
+        raise RuntimeError(f"reading the attention status failed with CUDA error {err}")
+    return tuple(out)
+
+
+def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: torch.Tensor, *,
+                    causal: bool = False, scale: Optional[float] = None) -> None:
+    global _last_runtime
+    assert Q.dim() == 4, "expected [B, H, S, D] tensors"
+    batch_size, num_heads, seq_len, d = Q.shape
+    assert Q.shape == K.shape == V.shape == Output.shape
+    assert Q.dtype == K.dtype == V.dtype == Output.dtype == torch.half
+    assert Q.device.type == "cuda", "flash_attn_cute has no CPU path"
+    assert Q.device == K.device == V.device == Output.device
+    if d not in SUPPORTED_HEAD_DIMS:
+        raise ValueError(f"head dim {d} not supported (supported: {SUPPORTED_HEAD_DIMS})")
+    if batch_size == 0 or num_heads == 0 or seq_len == 0:
+        return
+
+    q, k, v = (t if _usable_strides(t) else t.contiguous() for t in (Q, K, V))
+    out = Output if _usable_strides(Output) else torch.empty_like(Output, memory_format=torch.contiguous_format)
+
+    stream = torch.cuda.current_stream()
+    sm_scale = float(scale) if scale is not None else 1.0 / math.sqrt(d)
+
+    def pack(q, k, v, out):
+        strides = tuple(int(t.stride(i)) if t.shape[i] > 1 else 8 for t in (q, k, v, out) for i in range(3))
+        return (q, k, v, out, int(batch_size), int(num_heads), int(seq_len), *strides, bool(causal), sm_scale, stream)
+
+    args = pack(q, k, v, out)
+    runtime = jit_tuner.compile_and_tune(
+        name="flash_attn_cute",
+        keys={"D": d, "CAUSAL": int(bool(causal)), "CLASS": _seq_class(seq_len, batch_size * num_heads)},
+        space=tuning_space(d),
+        includes=includes,
+        arg_defs=arg_defs,
+        template=template,
+        args=args,
+        epilogue=epilogue,
+    )
+    _last_runtime = runtime
+
+    rc = runtime(*args)
+    if rc == _RC_TENSOR_MAP and not all(t.is_contiguous() for t in (q, k, v, out)):
+        # The layout cannot be described to the copy engine: fall back to packed copies.
+        q, k, v = (t.contiguous() for t in (q, k, v))
+        if not out.is_contiguous():
+            out = torch.empty_like(Output, memory_format=torch.contiguous_format)
+        rc = runtime(*pack(q, k, v, out))
+    if rc != 0:
+        raise RuntimeError(f"flash_attn_cute launch failed with code {rc} ({_RC_TEXT.get(rc, 'unknown')})")
+    if out is not Output:
+        Output.copy_(out)
