@@ -1,0 +1,298 @@
+"""Benchmark of the attention forward path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+One "step" is one forward pass of `flash_attn_cute` over the whole per-GPU workload.  The
+default workload is the shape the headline metric is quoted on: non-causal B=4, H=32,
+S=4096, D=128 (1.0995 TFLOP per step per GPU).  With N > 1 (launched by torchrun, one rank
+per GPU) every rank runs that workload on its own (b,h) units - the path shards by
+independent units, there is no collective on the data path - so scaling is weak and
+`value` is total FLOPs of all ranks over the slowest rank's device time.
+
+Prints ONE JSON line (rank 0).  `--impl reference` instead times the CPU oracle (torch CPU
+attention, the comparison the reference's own test uses) on a bounded sample of the same
+workload, on rank 0 only.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NOMINAL_FP16_TFLOPS = 2250.0
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+WORKLOADS = {
+    # name: (B, H, S, D, causal)
+    "headline": (4, 32, 4096, 128, False),
+    "c2": (2, 16, 2048, 128, False),
+    "c3": (4, 32, 4096, 128, True),
+    "c4": (1, 32, 16384, 128, True),
+    "c5": (16, 16, 1024, 64, False),
+}
+
+
+def flops_of(B, H, S, D, causal):
+    f = 4.0 * B * H * S * S * D
+    return f / 2 if causal else f
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            peaks = json.load(f)
+        return peaks, "measured"
+    except (OSError, ValueError):
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, universal_newlines=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        clocks, reasons, sm_max = [], set(), None
+        for sm, mx, hw, hwt, swt, pcap in self.rows:
+            try:
+                clocks.append(float(sm))
+                sm_max = float(mx)
+            except ValueError:
+                continue
+            for name, val in (("hw_slowdown", hw), ("hw_thermal_slowdown", hwt), ("sw_thermal_slowdown", swt),
+                              ("sw_power_cap", pcap)):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # the busy half of the samples is "under load"
+        busy = sorted(clocks)[len(clocks) // 2:] if clocks else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": sm_max,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def cpu_attention_sample(B, H, S, D, causal, budget_s=12.0, max_units=None):
+    """Times torch CPU attention (fp32 math on the fp16 inputs) on successive (b,h) units until the
+    budget is used; returns (TFLOP/s, units done, seconds, threads)."""
+    import torch.nn.functional as F
+    from oracle import attention_ref as ref
+    threads = torch.get_num_threads()
+    q, k, v = ref.make_slice(5, 0, S, D)
+    q, k, v = (t.float().reshape(1, 1, S, D) for t in (q, k, v))
+    F.scaled_dot_product_attention(q, k, v, is_causal=causal)  # warm-up
+    done, t0 = 0, time.perf_counter()
+    limit = max_units or B * H
+    while done < limit and (time.perf_counter() - t0) < budget_s:
+        F.scaled_dot_product_attention(q, k, v, is_causal=causal)
+        done += 1
+    dt = time.perf_counter() - t0
+    return flops_of(1, done, S, D, causal) / dt / 1e12, done, dt, threads
+
+
+def run_reference(args, B, H, S, D, causal, rank):
+    """CPU arm: torch CPU attention on a bounded sample of the workload, rank 0 only."""
+    if rank != 0:
+        return
+    import torch.nn.functional as F
+    from oracle import attention_ref as ref
+    threads = torch.get_num_threads()
+    units_per_step = 2
+    q, k, v = ref.make_inputs(5, range(units_per_step)) if (B, H, S, D) == (4, 32, 4096, 128) else tuple(
+        torch.randn(units_per_step, S, D).half() for _ in range(3))
+    q, k, v = (t.float().unsqueeze(0) for t in (q, k, v))
+    for _ in range(max(args.warmup, 1)):
+        F.scaled_dot_product_attention(q, k, v, is_causal=causal)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        F.scaled_dot_product_attention(q, k, v, is_causal=causal)
+    dt = time.perf_counter() - t0
+    value = flops_of(1, units_per_step, S, D, causal) * args.steps / dt / 1e12
+    sample = f"{units_per_step} of {B * H} (b,h) units per step, torch CPU scaled_dot_product_attention in fp32"
+    line = {
+        "impl": "reference", "metric": "flash_attn_fwd_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "B": B, "H": H, "S": S, "D": D, "causal": causal,
+                   "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="headline", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    B, H, S, D, causal = WORKLOADS[args.workload]
+
+    if args.impl == "reference":
+        run_reference(args, B, H, S, D, causal, rank)
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU: the attention path has no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
+    from fray_b200.jit_kernels.tuner import jit_tuner
+
+    # Synthetic inputs with the workload's shape and N(0,1) values, seeded per rank.
+    gen = torch.Generator(device="cuda").manual_seed(42 * 1000 + rank)
+    q, k, v = (torch.randn(B, H, S, D, generator=gen, device="cuda", dtype=torch.half) for _ in range(3))
+    out = torch.zeros_like(q)
+    flops = flops_of(B, H, S, D, causal)
+
+    def step():
+        flash_attn_cute(q, k, v, out, causal=causal)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step()  # JIT lookup + tuning happen here, outside every timed region
+    for _ in range(args.warmup):
+        step()
+    barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    stream = torch.cuda.current_stream()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    status = flash_attn_status()
+    assert status[0] == 0, f"device status {status}"
+
+    # ---- end to end: pinned host inputs -> device, op, result -> pinned host, every step
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    hout = torch.empty_like(hq).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        q.copy_(hq, non_blocking=True)
+        k.copy_(hk, non_blocking=True)
+        v.copy_(hv, non_blocking=True)
+        flash_attn_cute(q, k, v, out, causal=causal)
+        hout.copy_(out, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms_total = e0.elapsed_time(e1)
+
+    times = torch.tensor([ms_total / args.steps, e2e_ms_total / e2e_steps], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_step, e2e_ms_step = times.tolist()
+
+    if rank == 0:
+        peaks, peak_src = load_peaks()
+        value = flops * world / (ms_step * 1e-3) / 1e12
+        per_gpu = value / world
+        e2e_value = flops * world / (e2e_ms_step * 1e-3) / 1e12
+        peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        tuned = {str(sig[1]): keys for sig, keys in jit_tuner.tuned_keys.items()}
+        line = {
+            "metric": "flash_attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": args.workload, "B_per_gpu": B, "H": H, "S": S, "D": D, "causal": causal,
+                       "flops_per_step_per_gpu": flops, "l2": "inputs (537 MB per step) larger than the 126 MB L2"
+                       if B * H * S * D * 8 > 126e6 else "inputs smaller than L2, no flush",
+                       "kernel": tuned},
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
+                         "frac": per_gpu / peak, "traffic": None,
+                         "peak_source": f"{peak_src} sustained bf16 GEMM (steps run back to back)",
+                         "frac_of_nominal_2250": per_gpu / NOMINAL_FP16_TFLOPS,
+                         "frac_of_burst": per_gpu / float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms_step,
+                    "h2d_bytes_per_step": 3 * q.numel() * 2 * world, "d2h_bytes_per_step": out.numel() * 2 * world},
+            "gpu_launches": args.steps * world,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cpu_v, cpu_units, cpu_s, cpu_threads = cpu_attention_sample(B, H, S, D, causal)
+            line["cpu_baseline"] = {
+                "value": cpu_v, "unit": "TFLOP/s", "cores": cpu_threads, "kind": "port",
+                "sample": f"{cpu_units} of {B * H} (b,h) units in {cpu_s:.1f} s, torch CPU scaled_dot_product_attention "
+                          f"in fp32, host has {os.cpu_count()} logical cores"}
+        print(json.dumps(line), flush=True)
+
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -85,17 +85,27 @@ def _usable_strides(t: torch.Tensor) -> bool:
                for i in range(3))
 
 
-def prebuild(head_dims=SUPPORTED_HEAD_DIMS) -> int:
-    """Compile every point of the tuning space ahead of time; returns how many kernels exist afterwards."""
+def prebuild(head_dims=SUPPORTED_HEAD_DIMS, prune: bool = False):
+    """Compile every point of the tuning space ahead of time and return the kernel directories.
+
+    With ``prune`` the cache directory is also cleared of attention kernels that no longer
+    belong to the space (left over from older headers).
+    """
+    import shutil
     from ..jit import build, cpp_format, generate
-    count = 0
+    from ..jit.compiler import get_cache_dir
+    paths = []
     for d in head_dims:
         for point in tuning_space(d):
             keys = {"D": d, **point}
             code = generate(includes, arg_defs, cpp_format(template, keys), cpp_format(epilogue, keys))
-            build("flash_attn_cute", arg_defs, code)
-            count += 1
-    return count
+            paths.append(build("flash_attn_cute", arg_defs, code).path)
+    if prune:
+        for entry in os.listdir(get_cache_dir()):
+            full = os.path.join(get_cache_dir(), entry)
+            if entry.startswith("kernel.flash_attn_cute.") and full not in paths:
+                shutil.rmtree(full, ignore_errors=True)
+    return paths
 
 
 _last_runtime = None
@@ -148,7 +158,8 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
     args = pack(q, k, v, out)
     runtime = jit_tuner.compile_and_tune(
         name="flash_attn_cute",
-        keys={"D": d, "CAUSAL": int(bool(causal)), "CLASS": _seq_class(seq_len, batch_size * num_heads)},
+        keys={"D": d, "CAUSAL": int(bool(causal)), "CLASS": _seq_class(seq_len, batch_size * num_heads),
+              "FORCED": os.getenv("FRAY_ATTN_FORCE", "")},
         space=tuning_space(d),
         includes=includes,
         arg_defs=arg_defs,

@@ -1,0 +1,55 @@
+/* C ABI of one built attention kernel library (kernel.so).
+ *
+ * Every library produced by the JIT for `flash_attn_cute` exports the symbols below with
+ * C linkage.  They replace what the reference runtime binds through ctypes
+ * (fray/jit/runtime.py:30-68): a single `launch` whose prototype is generated from the
+ * op's argument table (fray/jit/template.py:130-149, fray/jit_kernels/flashattn_cute.py:40).
+ * All pointers are plain device or host addresses; no framework types cross the boundary.
+ * The caller owns every buffer; the library allocates nothing and keeps no pointers.
+ */
+#ifndef FRAY_B200_ATTN_H_
+#define FRAY_B200_ATTN_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Queue the attention forward  O = softmax(scale * Q K^T [+ causal mask]) V  on `stream`.
+ *
+ * Replaces: launch(void* Q, void* K, void* V, void* O, int batch_size, int num_heads,
+ *                  int seq_len, void* stream, int& __return_code)
+ * generated for fray::flash_attn_cute<R,C,D> (fray/include/flash_attn/flashattn_cute.cuh:166-239).
+ * Added over the reference prototype: element strides of the batch, head and sequence
+ * modes of each tensor (the head-dim stride is 1), the causal flag and the softmax scale,
+ * which the reference fixed to contiguous / false / 1/sqrt(D).
+ *
+ * Q, K, V, O   fp16 device pointers, 16-byte aligned, logical shape [batch, heads, seq, D]
+ *              where D is the head dim the library was built for (fray_attn_kernel_info).
+ * *_stride_*   in elements, positive multiples of 8 (ignored for modes of extent 1).
+ * stream       a cudaStream_t; the call returns once the kernel is queued.
+ * __return_code receives 0 when the kernel was queued, otherwise (nothing launched):
+ *              1 bad shape, 2 bad pointer, 3 bad stride, 5 driver entry point missing,
+ *              6 tensor map rejected, 7 shared-memory attribute failed, 8 launch failed.
+ */
+void launch(void* Q, void* K, void* V, void* O, int batch_size, int num_heads, int seq_len,
+            int q_stride_b, int q_stride_h, int q_stride_s, int k_stride_b, int k_stride_h, int k_stride_s,
+            int v_stride_b, int v_stride_h, int v_stride_s, int o_stride_b, int o_stride_h, int o_stride_s,
+            bool causal, float scale, void* stream, int* __return_code);
+
+/* Blocking read of the sticky device status: out4[0] is 0 when healthy, else the code of
+ * the first in-kernel wait that ran out; out4[1..3] are block x, block y and an iteration
+ * index.  While out4[0] != 0 later launches of this library return without computing;
+ * pass clear != 0 to reset.  Returns 0 or a cudaError_t value.
+ * No counterpart in the reference, which never checks device-side errors
+ * (fray/jit_kernels/tuner.py:45-50 only sees the always-zero return code). */
+int fray_attn_status(int* out4, int clear);
+
+/* out4 = {kernel kind, head dim D, KV tile length, KV pipeline stages} this library was
+ * instantiated with - the template keys the reference keeps only in the source text
+ * (fray/jit_kernels/flashattn_cute.py:32-38). */
+void fray_attn_kernel_info(int* out4);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRAY_B200_ATTN_H_ */

@@ -1,0 +1,55 @@
+"""Every built attention library loads and exports what include/fray_b200_attn.h declares.
+
+No compute is launched: `launch` is only called with arguments it must reject before it
+touches the CUDA runtime.
+"""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "fray_b200_attn.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"^\s*(?:void|int)\s+(\w+)\s*\(", text, flags=re.M)))
+
+
+def test_header_declares_the_expected_entry_points():
+    assert declared_symbols() == ["fray_attn_kernel_info", "fray_attn_status", "launch"]
+
+
+def test_every_library_exports_every_declared_symbol(built_kernels):
+    assert len(built_kernels) >= 4
+    seen = set()
+    for path in built_kernels:
+        lib = ctypes.CDLL(os.path.join(path, "kernel.so"))
+        for name in declared_symbols():
+            assert hasattr(lib, name), f"{path} lacks {name}"
+        info = (ctypes.c_int * 4)()
+        lib.fray_attn_kernel_info(info)
+        assert info[1] in (64, 128) and info[2] in (64, 128)
+        seen.add(tuple(info))
+    assert len(seen) == len(built_kernels)  # one library per point of the space
+
+
+def _call(lib, q=0x1000, k=0x1000, v=0x1000, o=0x1000, B=1, H=1, S=128, strides=None):
+    strides = strides or [8192, 8192, 64] * 4
+    rc = ctypes.c_int(-1)
+    lib.launch(ctypes.c_void_p(q), ctypes.c_void_p(k), ctypes.c_void_p(v), ctypes.c_void_p(o), B, H, S,
+               *strides, ctypes.c_bool(False), ctypes.c_float(0.125), ctypes.c_void_p(0), ctypes.byref(rc))
+    return rc.value
+
+
+def test_launch_rejects_bad_arguments_without_touching_the_gpu(built_kernels):
+    lib = ctypes.CDLL(os.path.join(built_kernels[0], "kernel.so"))
+    assert _call(lib, B=0) == 1
+    assert _call(lib, S=-5) == 1
+    assert _call(lib, q=0) == 2
+    assert _call(lib, o=0x1008) == 2            # not 16-byte aligned
+    assert _call(lib, S=256, strides=[8192, 8192, 60] + [8192, 8192, 64] * 3) == 3   # 60 elements = 120 bytes
+    assert _call(lib, S=256, B=2, strides=[0, 8192, 64] + [8192, 8192, 64] * 3) == 3

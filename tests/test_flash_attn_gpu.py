@@ -1,0 +1,244 @@
+"""Parity of the CUDA attention path with the CPU oracle, through the public op (which calls
+the C ABI `launch` of the selected kernel library).
+
+Tolerances are the ones the path is specified with: max|out - torch fp16 attention| <= 1e-2
+(the reference test's criterion, tests/test_flashattn_cute.py:27-28) and
+calc_diff(out, fp32 attention) <= 1e-5.
+"""
+import ctypes
+import math
+import os
+
+import pytest
+import torch
+
+from oracle import attention_ref as ref
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 1e-2
+MAX_DIFF = 1e-5
+
+
+def all_variants():
+    from fray_b200.jit_kernels.flashattn_cute import tuning_space
+    old = os.environ.pop("FRAY_ATTN_FORCE", None)
+    try:
+        pts = {tuple(sorted(p.items())) for d in (64, 128) for p in tuning_space(d)}
+    finally:
+        if old is not None:
+            os.environ["FRAY_ATTN_FORCE"] = old
+    return [",".join(f"{k}={v}" for k, v in p) for p in sorted(pts)]
+
+
+@pytest.fixture(params=["tuned"] + all_variants())
+def variant(request, monkeypatch):
+    if request.param != "tuned":
+        monkeypatch.setenv("FRAY_ATTN_FORCE", request.param)
+    else:
+        monkeypatch.delenv("FRAY_ATTN_FORCE", raising=False)
+    return request.param
+
+
+def run_op(q, k, v, causal=False, scale=None, out=None):
+    """q,k,v: CUDA fp16 [B,H,S,D] (any supported strides). Returns the output tensor after a status check."""
+    from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
+    out = torch.zeros_like(q) if out is None else out
+    flash_attn_cute(q, k, v, out, causal=causal, scale=scale)
+    torch.cuda.synchronize()
+    status = flash_attn_status()
+    assert status[0] == 0, f"device status {status}"
+    return out
+
+
+def check(out, q, k, v, causal, scale=None):
+    out = out.cpu()
+    q, k, v = (t.cpu() for t in (q, k, v))
+    assert not torch.isnan(out).any()
+    max_abs = (out.float() - ref.sdpa_cpu(q, k, v, causal, scale).float()).abs().max().item()
+    diff = ref.calc_diff(out, ref.attention_fp32(q, k, v, causal, scale))
+    assert max_abs <= MAX_ABS, f"max abs {max_abs}"
+    assert diff <= MAX_DIFF, f"calc_diff {diff}"
+
+
+def config_tensors(ci, units=None):
+    cfg = ref.CONFIGS[ci]
+    q, k, v = ref.make_inputs(ci, units)
+    n = q.shape[0]
+    if units is None:
+        shape = (cfg["B"], cfg["H"], cfg["S"], cfg["D"])
+    else:
+        shape = (1, n, cfg["S"], cfg["D"])
+    return tuple(t.reshape(shape).cuda() for t in (q, k, v)), cfg
+
+
+# ---------------------------------------------------------------- BASELINE configurations
+def test_config1_plumbing(variant):
+    (q, k, v), cfg = config_tensors(0)
+    check(run_op(q, k, v), q, k, v, False)
+    check(run_op(q, k, v, causal=True), q, k, v, True)
+
+
+def test_config2_readme_shape(variant):
+    (q, k, v), cfg = config_tensors(1)
+    assert q.shape == (2, 16, 2048, 128)
+    check(run_op(q, k, v), q, k, v, False)
+
+
+def test_config3_causal_sampled_units():
+    # Full size on the GPU; the oracle checks the first, a middle and the last (b,h) unit.
+    cfg = ref.CONFIGS[2]
+    units = [0, 61, 127]
+    (q, k, v), _ = config_tensors(2, units)
+    out = run_op(q, k, v, causal=True)
+    check(out, q, k, v, True)
+
+
+def test_config4_long_context_one_head():
+    (q, k, v), cfg = config_tensors(3, [7])
+    assert q.shape[2] == 16384
+    out = run_op(q, k, v, causal=True)
+    check(out, q, k, v, True)
+
+
+def test_config5_large_logits_and_transposed_q(variant):
+    cfg = ref.CONFIGS[4]
+    units = list(range(2 * cfg["H"]))               # two batches, all heads
+    q, k, v = ref.make_inputs(4, units)
+    B, H, S, D = 2, cfg["H"], cfg["S"], cfg["D"]
+    q, k, v = (t.reshape(B, H, S, D) for t in (q, k, v))
+    q_bshd = q.permute(0, 2, 1, 3).contiguous().cuda()      # storage [B,S,H,D]
+    q_view = q_bshd.transpose(1, 2)                          # logical [B,H,S,D], non-contiguous
+    assert not q_view.is_contiguous()
+    out = run_op(q_view, k.cuda(), v.cuda())
+    check(out, q, k, v, False)
+
+
+# ---------------------------------------------------------------- edge cases
+@pytest.mark.parametrize("S", [128, 256, 384])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+def test_small_sequences(variant, S, D, causal):
+    g = torch.Generator().manual_seed(S * 7 + D)
+    q, k, v = (torch.randn(2, 3, S, D, generator=g).half().cuda() for _ in range(3))
+    check(run_op(q, k, v, causal=causal), q, k, v, causal)
+
+
+@pytest.mark.parametrize("S", [1, 17, 127, 129, 200, 333])
+@pytest.mark.parametrize("causal", [False, True])
+def test_ragged_sequence_lengths(variant, S, causal):
+    g = torch.Generator().manual_seed(S)
+    q, k, v = (torch.randn(1, 2, S, 64, generator=g).half().cuda() for _ in range(3))
+    guard = torch.full((1, 2, S + 8, 64), 7.0, dtype=torch.half, device="cuda")
+    out = guard[:, :, :S]                       # rows past S must stay untouched
+    run_op(q, k, v, causal=causal, out=out)
+    check(out, q, k, v, causal)
+    assert (guard[:, :, S:] == 7.0).all()
+
+
+def test_causal_first_row_copies_v0_and_last_row_sees_everything(variant):
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(1, 1, 512, 128, generator=g).half().cuda() for _ in range(3))
+    out = run_op(q, k, v, causal=True)
+    assert torch.equal(out[0, 0, 0], v[0, 0, 0])            # softmax over one key
+    full = run_op(q, k, v, causal=False)
+    assert (out[0, 0, -1].float() - full[0, 0, -1].float()).abs().max() <= 2e-3
+
+
+def test_noncontiguous_output_receives_result(variant):
+    g = torch.Generator().manual_seed(9)
+    q, k, v = (torch.randn(2, 4, 256, 64, generator=g).half().cuda() for _ in range(3))
+    store = torch.zeros(2, 256, 4, 64, dtype=torch.half, device="cuda")
+    out_view = store.transpose(1, 2)
+    run_op(q, k, v, out=out_view)
+    check(out_view, q, k, v, False)
+    assert store.abs().sum() > 0
+
+
+def test_explicit_scale(variant):
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(1, 2, 256, 128, generator=g).half().cuda() for _ in range(3))
+    check(run_op(q, k, v, scale=0.05), q, k, v, False, scale=0.05)
+
+
+def test_runs_on_the_current_stream(variant):
+    g = torch.Generator().manual_seed(13)
+    q, k, v = (torch.randn(1, 2, 256, 64, generator=g).half().cuda() for _ in range(3))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        out = run_op(q, k, v)
+    check(out, q, k, v, False)
+
+
+def test_unsupported_head_dim_raises():
+    from fray_b200.jit_kernels import flash_attn_cute
+    t = torch.zeros(1, 1, 128, 96, dtype=torch.half, device="cuda")
+    with pytest.raises(ValueError):
+        flash_attn_cute(t, t, t, t.clone())
+
+
+# ---------------------------------------------------------------- direct C-ABI call
+def test_direct_c_abi_call(built_kernels):
+    g = torch.Generator().manual_seed(21)
+    for path in built_kernels:
+        lib = ctypes.CDLL(os.path.join(path, "kernel.so"))
+        info = (ctypes.c_int * 4)()
+        lib.fray_attn_kernel_info(info)
+        D = info[1]
+        q, k, v = (torch.randn(1, 2, 256, D, generator=g).half().cuda() for _ in range(3))
+        out = torch.zeros_like(q)
+        st = [2 * 256 * D, 256 * D, D] * 4
+        rc = ctypes.c_int(-1)
+        lib.launch(*(ctypes.c_void_p(t.data_ptr()) for t in (q, k, v, out)), 1, 2, 256, *st, ctypes.c_bool(True),
+                   ctypes.c_float(1.0 / math.sqrt(D)), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+                   ctypes.byref(rc))
+        assert rc.value == 0
+        torch.cuda.synchronize()
+        status = (ctypes.c_int * 4)()
+        assert lib.fray_attn_status(status, 1) == 0 and status[0] == 0
+        check(out, q, k, v, True)
+
+
+# ---------------------------------------------------------------- properties at full size
+def test_headline_size_properties():
+    """B=4,H=32,S=4096,D=128 non-causal: properties that need no CPU attention at that size."""
+    B, H, S, D = 4, 32, 4096, 128
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randn(B, H, S, D, generator=g, device="cuda", dtype=torch.half)
+    k = torch.randn(B, H, S, D, generator=g, device="cuda", dtype=torch.half)
+    v = torch.randn(B, H, S, D, generator=g, device="cuda", dtype=torch.half)
+    out = run_op(q, k, v)
+    # (1) every output lies inside the per-column range of V (softmax weights are convex)
+    assert (out.float() <= v.float().amax(dim=2, keepdim=True) + 1e-2).all()
+    assert (out.float() >= v.float().amin(dim=2, keepdim=True) - 1e-2).all()
+    # (2) a constant V comes back unchanged
+    const_v = torch.full_like(v, 0.75)
+    assert (run_op(q, k, const_v).float() - 0.75).abs().max() <= 2e-3
+    # (3) permuting the keys (with their values) does not change a non-causal result
+    perm = torch.randperm(S, generator=torch.Generator().manual_seed(1)).cuda()
+    out_p = run_op(q, k[:, :, perm].contiguous(), v[:, :, perm].contiguous())
+    assert (out_p.float() - out.float()).abs().max() <= 4e-3
+    # (4) linear in V
+    v2 = torch.randn(B, H, S, D, generator=g, device="cuda", dtype=torch.half)
+    lhs = run_op(q, k, (v.float() * 0.5 + v2.float()).half())
+    rhs = 0.5 * out.float() + run_op(q, k, v2).float()
+    assert (lhs.float() - rhs).abs().max() <= 1e-2
+    # (5) one (b,h) unit against the oracle
+    check(out[1:2, 5:6], q[1:2, 5:6], k[1:2, 5:6], v[1:2, 5:6], False)
+    # (6) determinism
+    assert torch.equal(out, run_op(q, k, v))
+
+
+def test_causality_at_full_length():
+    """Changing keys/values after position p must not change outputs up to p (S=4096 causal)."""
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q, k, v = (torch.randn(1, 4, 4096, 128, generator=g, device="cuda", dtype=torch.half) for _ in range(3))
+    out = run_op(q, k, v, causal=True)
+    p = 1500
+    k2, v2 = k.clone(), v.clone()
+    k2[:, :, p + 1:] = 3.0
+    v2[:, :, p + 1:] = -2.0
+    out2 = run_op(q, k2, v2, causal=True)
+    assert torch.equal(out[:, :, :p + 1], out2[:, :, :p + 1])
+    assert not torch.equal(out[:, :, p + 1:], out2[:, :, p + 1:])
