@@ -38,6 +38,9 @@ WORKLOADS = {
     "c3": (4, 32, 4096, 128, True),
     "c4": (1, 32, 16384, 128, True),
     "c5": (16, 16, 1024, 64, False),
+    # one batch of the headline shape: 134 MB of operands (> L2), small enough for profiler captures
+    "small": (1, 32, 4096, 128, False),
+    "small_causal": (1, 32, 4096, 128, True),
 }
 
 
@@ -57,62 +60,69 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML from a thread while the timed region runs."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, period_s: float = 0.002):
         self.gpu_index = gpu_index
-        self.rows = []
-        self.proc = None
+        self.period_s = period_s
+        self.samples = []       # (sm_mhz, reasons bitmask)
+        self.sm_max = None
+        self._stop = threading.Event()
         self.thread = None
+        self.error = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, universal_newlines=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.gpu_index
+            if visible:
+                entry = visible.split(",")[self.gpu_index].strip()
+                index = int(entry) if entry.isdigit() else self.gpu_index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+        except Exception as exc:  # NVML missing: report it, do not fail the benchmark
+            self.error = repr(exc)
             return
-        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
 
-    def _pump(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6:
-                self.rows.append(parts)
+    def _loop(self):
+        nv = self.nvml
+        while not self._stop.is_set():
+            try:
+                clk = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                why = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                self.samples.append((float(clk), int(why)))
+            except Exception as exc:
+                self.error = repr(exc)
+                return
+            time.sleep(self.period_s)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+        self._stop.set()
         if self.thread is not None:
             self.thread.join(timeout=2)
-        clocks, reasons, sm_max = [], set(), None
-        for sm, mx, hw, hwt, swt, pcap in self.rows:
-            try:
-                clocks.append(float(sm))
-                sm_max = float(mx)
-            except ValueError:
-                continue
-            for name, val in (("hw_slowdown", hw), ("hw_thermal_slowdown", hwt), ("sw_thermal_slowdown", swt),
-                              ("sw_power_cap", pcap)):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        # the busy half of the samples is "under load"
-        busy = sorted(clocks)[len(clocks) // 2:] if clocks else []
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": sm_max,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.sm_max, "reasons": [f"no samples: {self.error}"], "samples": 0}
+        nv = self.nvml
+        names = {
+            "hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+            "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+            "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+            "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap,
+        }
+        seen = 0
+        for _, why in self.samples:
+            seen |= why
+        reasons = sorted(n for n, bit in names.items() if seen & bit)
+        return {"sm_mhz": statistics.median(c for c, _ in self.samples), "sm_max_mhz": self.sm_max,
+                "reasons": reasons, "samples": len(self.samples)}
 
 
-def cpu_attention_sample(B, H, S, D, causal, budget_s=12.0, max_units=None):
+def cpu_attention_sample(B, H, S, D, causal, budget_s=12.0):
     """Times torch CPU attention (fp32 math on the fp16 inputs) on successive (b,h) units until the
     budget is used; returns (TFLOP/s, units done, seconds, threads)."""
     import torch.nn.functional as F
@@ -122,8 +132,7 @@ def cpu_attention_sample(B, H, S, D, causal, budget_s=12.0, max_units=None):
     q, k, v = (t.float().reshape(1, 1, S, D) for t in (q, k, v))
     F.scaled_dot_product_attention(q, k, v, is_causal=causal)  # warm-up
     done, t0 = 0, time.perf_counter()
-    limit = max_units or B * H
-    while done < limit and (time.perf_counter() - t0) < budget_s:
+    while (time.perf_counter() - t0) < budget_s:
         F.scaled_dot_product_attention(q, k, v, is_causal=causal)
         done += 1
     dt = time.perf_counter() - t0
@@ -170,6 +179,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="headline", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true", help="skip the end-to-end and CPU legs (profiler runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -229,6 +239,13 @@ def main():
     assert status[0] == 0, f"device status {status}"
 
     # ---- end to end: pinned host inputs -> device, op, result -> pinned host, every step
+    if args.kernel_only:
+        if rank == 0:
+            value = flops * world / (ms_total / args.steps * 1e-3) / 1e12
+            print(json.dumps({"metric": "flash_attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                              "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_total / args.steps,
+                              "config": {"workload": args.workload}, "kernel_only": True, "clocks": clocks}), flush=True)
+        return
     hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
     hout = torch.empty_like(hq).pin_memory()
     e2e_steps = max(3, min(args.steps, 10))
@@ -285,8 +302,8 @@ def main():
             cpu_v, cpu_units, cpu_s, cpu_threads = cpu_attention_sample(B, H, S, D, causal)
             line["cpu_baseline"] = {
                 "value": cpu_v, "unit": "TFLOP/s", "cores": cpu_threads, "kind": "port",
-                "sample": f"{cpu_units} of {B * H} (b,h) units in {cpu_s:.1f} s, torch CPU scaled_dot_product_attention "
-                          f"in fp32, host has {os.cpu_count()} logical cores"}
+                "sample": f"{cpu_units} single-(b,h)-unit passes (the workload has {B * H} units) in {cpu_s:.1f} s, torch CPU "
+                          f"scaled_dot_product_attention in fp32, host has {os.cpu_count()} logical cores"}
         print(json.dumps(line), flush=True)
 
     if dist is not None:

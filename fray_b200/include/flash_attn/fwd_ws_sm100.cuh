@@ -1,0 +1,427 @@
+#pragma once
+// Warp-specialised attention forward for sm_100a.
+//
+// One CTA of 16 warps owns two 128-row query tiles of one (batch, head) slice:
+//   warps 0-3   softmax group 0 (query tile 0; thread r owns row r)
+//   warps 4-7   softmax group 1 (query tile 1)
+//   warps 8-11  correction group: rescales the O accumulators when a running max moved,
+//               and runs the epilogue (O/l -> fp16 -> shared memory -> TMA store)
+//   warp 12     MMA issue (one thread issues every tcgen05.mma / commit)
+//   warp 13     TMA producer (Q tiles once, then K_j, V_j through a ring of STAGES buffers)
+//   warps 14-15 idle (they only exist so that warps 12-15 form a full warpgroup for setmaxnreg)
+//
+// Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512).  P (fp16)
+// overwrites the first 64 columns of its S buffer and is consumed from there as the A
+// operand of the P.V product; the tensor pipe executes MMAs in issue order, so the next
+// S = Q.K^T of that tile may be issued right behind it.
+//
+// Issue order in the MMA warp: S0(0) S1(0) | PV0(0) S0(1) PV1(0) S1(1) | PV0(1) S0(2) ...
+// so that while group 0 runs the softmax of S0(j+1) the tensor cores work on PV1(j) and
+// S1(j+1), and vice versa.
+//
+// Online softmax in base 2 with lazy rescaling: a tile's exponent offset m_ref only moves
+// when the running max grew by more than 2^8 in the scaled domain; until then P may exceed
+// 1 (at most 256, exact in fp16 range) and O needs no correction.  O and l always share the
+// same m_ref, so the final O/l is the exact softmax up to rounding.
+//
+// Every barrier wait is bounded (see sm100_ptx.cuh): a protocol error ends as a status
+// word and a wrong answer, never as a hung GPU.
+
+#include "host_sm100.cuh"
+#include "sm100_ptx.cuh"
+
+namespace fray {
+namespace sm100 {
+
+template <int D, int BN, int STAGES>
+struct WsCfg {
+  static_assert(D == 64 || D == 128, "head dim must be 64 or 128");
+  static_assert(BN == 128, "the warp-specialised kernel uses 128-key tiles");
+  static_assert(STAGES >= 2 && STAGES <= 8, "2..8 K/V buffers");
+  static constexpr int BM = 128;               // rows per query tile
+  static constexpr int kThreads = 512;
+  static constexpr int kPanels = D / 64;       // 64-element (128-byte) column panels
+  static constexpr int kQPanelBytes = BM * 128;
+  static constexpr int kQTileBytes = kPanels * kQPanelBytes;
+  static constexpr int kKVPanelBytes = BN * 128;
+  static constexpr int kKVTileBytes = kPanels * kKVPanelBytes;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffKV = 2 * kQTileBytes;
+  static constexpr int kOffBars = kOffKV + STAGES * kKVTileBytes;
+  static constexpr int kNumBars = 2 + 2 * STAGES + 2 * 5;
+  static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][128], l[2][128]
+  static constexpr int kSmemBytes = kOffStats + 4 * 128 * 4 + 1024;                    // + alignment slack
+  static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of one CTA");
+  static constexpr int kTmemCols = 512;
+  static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+  // register budgets after setmaxnreg (sum over 16 warps = 64K registers)
+  static constexpr int kRegsSoftmax = 184, kRegsCorrection = 80, kRegsOther = 64;
+};
+
+template <int N>
+__device__ __forceinline__ void set_max_regs_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void set_max_regs_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Lazy-rescale threshold in the scaled base-2 domain: offsets move only when the max grew by > 2^8.
+static constexpr float kRescaleThreshold = 8.0f;
+
+template <int D, int BN, int STAGES>
+__global__ void __launch_bounds__(512, 1)
+attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+                   int num_heads, int seq_len, int causal, float scale_log2) {
+  using Cfg = WsCfg<D, BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* q_smem = smem + Cfg::kOffQ;    // tile i at q_smem + i * kQTileBytes (reused for the O tile at the end)
+  uint8_t* kv_smem = smem + Cfg::kOffKV;  // ring slot s at kv_smem + s * kKVTileBytes
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
+  uint64_t* q_full = bars;                      // [2]   producer -> MMA
+  uint64_t* kv_full = bars + 2;                 // [STAGES] producer -> MMA
+  uint64_t* kv_empty = kv_full + STAGES;        // [STAGES] MMA -> producer
+  uint64_t* s_full = kv_empty + STAGES;         // [2]   MMA -> softmax i        (S_i(j) complete)
+  uint64_t* p_full = s_full + 2;                // [2]   softmax i -> MMA        (P_i(j) stored)
+  uint64_t* o_full = p_full + 2;                // [2]   MMA -> correction       (PV_i(j) complete)
+  uint64_t* corr_ready = o_full + 2;            // [2]   softmax i -> correction (alpha_i(j) / final l published)
+  uint64_t* o_rescaled = corr_ready + 2;        // [2]   correction -> MMA       (O_i ready for PV_i(j))
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+  float* alpha_buf = reinterpret_cast<float*>(smem + Cfg::kOffStats);  // [2][128]
+  float* l_buf = alpha_buf + 256;                                      // [2][128]
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int pair = causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heaviest causal tiles first
+  const int m0 = pair * (2 * Cfg::BM);
+  const int bh = blockIdx.y;
+  const int b = bh / num_heads;
+  const int h = bh - b * num_heads;
+
+  // Number of KV tiles each query tile consumes (0 = tile lies past the end of the sequence).
+  const int n_kv = (seq_len + BN - 1) / BN;
+  int n_t[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row0 = m0 + i * Cfg::BM;
+    int n = row0 < seq_len ? n_kv : 0;
+    if (causal && n > 0) {
+      const int lim = (row0 + Cfg::BM + BN - 1) / BN;
+      n = lim < n ? lim : n;
+    }
+    n_t[i] = n;
+  }
+  const int n_max = n_t[0] > n_t[1] ? n_t[0] : n_t[1];
+
+  if (tid == 0) {
+    *abort_flag = (*reinterpret_cast<volatile int*>(&fray_attn_status[0]) != 0) ? 2u : 0u;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(q_full + i, 1);
+      mbar_init(s_full + i, 1);
+      mbar_init(p_full + i, 128);
+      mbar_init(o_full + i, 1);
+      mbar_init(corr_ready + i, 128);
+      mbar_init(o_rescaled + i, 128);
+    }
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(kv_full + s, 1);
+      mbar_init(kv_empty + s, 1);
+    }
+    fence_barrier_init();
+    prefetch_tensormap(&tm_q);
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
+    prefetch_tensormap(&tm_o);
+  }
+  __syncthreads();
+  if (*abort_flag != 0) return;  // an earlier launch left the device status raised
+
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 8) {
+    // =============================================================== softmax groups
+    set_max_regs_inc<Cfg::kRegsSoftmax>();
+    const int i = warp >> 2;              // query tile of this group
+    const int r = tid & 127;              // row inside the tile
+    const int n_i = n_t[i];
+    const int row = m0 + i * Cfg::BM + r;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1) + lane_base;
+    float m_ref = -INFINITY;  // exponent offset currently baked into P, l and O
+    float l_run = 0.f;
+
+    for (int j = 0; j < n_i; ++j) {
+      mbar_wait(s_full + i, j & 1, abort_flag, 0x201 + i, j);
+      tc_fence_after_sync();
+      uint32_t sr[BN];
+#pragma unroll
+      for (int c = 0; c < BN / 32; ++c) tmem_ld_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
+      tmem_wait_ld();
+
+      const int kv0 = j * BN;
+      if ((kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM))) {
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
+          const int kv = kv0 + c;
+          if (kv >= seq_len || (causal && kv > row)) sr[c] = __float_as_uint(-INFINITY);
+        }
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < BN; c += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sr[c + 0]));
+        mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+      }
+      const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m_ref);
+
+      if (j == 0) {
+        m_ref = m_new;
+      } else {
+        float alpha = 1.f;
+        if ((m_new - m_ref) * scale_log2 > kRescaleThreshold) {
+          alpha = ex2_approx((m_ref - m_new) * scale_log2);
+          l_run *= alpha;
+          m_ref = m_new;
+        }
+        alpha_buf[i * 128 + r] = alpha;
+        mbar_arrive(corr_ready + i);
+      }
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
+
+      float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+      for (int c = 0; c < BN; c += 2) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c]), scale_log2, neg_m));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 1]), scale_log2, neg_m));
+        rs0 += p0;
+        rs1 += p1;
+        sr[c >> 1] = pack_half2(p0, p1);
+      }
+      l_run += rs0 + rs1;
+#pragma unroll
+      for (int c = 0; c < BN / 64; ++c) tmem_st_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(p_full + i);
+    }
+    if (n_i > 0) {
+      l_buf[i * 128 + r] = l_run;
+      mbar_arrive(corr_ready + i);
+    }
+  } else if (warp < 12) {
+    // =============================================================== correction group + epilogue
+    set_max_regs_dec<Cfg::kRegsCorrection>();
+    const int r = tid & 127;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    for (int j = 1; j < n_max; ++j) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        if (j < n_t[i]) {
+          const uint32_t ph = (j - 1) & 1;
+          mbar_wait(corr_ready + i, ph, abort_flag, 0x301 + i, j);
+          const float alpha = alpha_buf[i * 128 + r];
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            mbar_wait(o_full + i, ph, abort_flag, 0x311 + i, j);
+            tc_fence_after_sync();
+            const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1) + lane_base;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t orr[32];
+              tmem_ld_x32(t_o + c * 32, orr);
+              tmem_wait_ld();
+#pragma unroll
+              for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha);
+              tmem_st_x32(t_o + c * 32, orr);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+          }
+          mbar_arrive(o_rescaled + i);
+        }
+      }
+    }
+    // Epilogue: O_i / l_i -> fp16 -> shared memory (the dead Q_i buffer, 128B-swizzled) -> TMA store.
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int n_i = n_t[i];
+      if (n_i > 0) {
+        const uint32_t ph = (n_i - 1) & 1;
+        mbar_wait(corr_ready + i, ph, abort_flag, 0x321 + i, n_i);
+        const float l = l_buf[i * 128 + r];
+        const float inv_l = l > 0.f ? 1.f / l : 1.f;
+        mbar_wait(o_full + i, ph, abort_flag, 0x331 + i, n_i);
+        tc_fence_after_sync();
+        const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1) + lane_base;
+        uint8_t* o_tile = q_smem + i * Cfg::kQTileBytes;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orr[32];
+          tmem_ld_x32(t_o + c * 32, orr);
+          tmem_wait_ld();
+          uint8_t* panel_row = o_tile + (c >> 1) * Cfg::kQPanelBytes + r * 128;
+#pragma unroll
+          for (int x = 0; x < 32; x += 8) {
+            uint4 v4;
+            v4.x = pack_half2(__uint_as_float(orr[x + 0]) * inv_l, __uint_as_float(orr[x + 1]) * inv_l);
+            v4.y = pack_half2(__uint_as_float(orr[x + 2]) * inv_l, __uint_as_float(orr[x + 3]) * inv_l);
+            v4.z = pack_half2(__uint_as_float(orr[x + 4]) * inv_l, __uint_as_float(orr[x + 5]) * inv_l);
+            v4.w = pack_half2(__uint_as_float(orr[x + 6]) * inv_l, __uint_as_float(orr[x + 7]) * inv_l);
+            const int chunk = (c & 1) * 4 + (x >> 3);  // 16-byte chunk inside the 128-byte row
+            *reinterpret_cast<uint4*>(panel_row + ((chunk ^ (r & 7)) << 4)) = v4;
+          }
+        }
+        fence_proxy_async_smem();
+        named_barrier_sync(1, 128);
+        if (r == 0) {
+#pragma unroll
+          for (int p = 0; p < Cfg::kPanels; ++p)
+            tma_store_4d(&tm_o, o_tile + p * Cfg::kQPanelBytes, p * 64, m0 + i * Cfg::BM, h, b);
+          tma_store_commit();
+        }
+      }
+    }
+    if (r == 0) tma_store_wait_all();
+  } else {
+    set_max_regs_dec<Cfg::kRegsOther>();
+    if (warp == 13 && lane == 0) {
+      // ============================================================= TMA producer
+      auto load_q = [&](int i) {
+        if (n_t[i] > 0) {
+          mbar_expect_tx(q_full + i, Cfg::kQTileBytes);
+#pragma unroll
+          for (int p = 0; p < Cfg::kPanels; ++p)
+            tma_load_4d(q_smem + i * Cfg::kQTileBytes + p * Cfg::kQPanelBytes, &tm_q, q_full + i, p * 64,
+                        m0 + i * Cfg::BM, h, b);
+        }
+      };
+      load_q(0);
+      for (int t = 0; t < 2 * n_max; ++t) {
+        const int slot = t % STAGES;
+        const uint32_t ph = (t / STAGES) & 1;
+        mbar_wait(kv_empty + slot, ph ^ 1, abort_flag, 0x401, t);
+        mbar_expect_tx(kv_full + slot, Cfg::kKVTileBytes);
+        const CUtensorMap* tm = (t & 1) ? &tm_v : &tm_k;
+#pragma unroll
+        for (int p = 0; p < Cfg::kPanels; ++p)
+          tma_load_4d(kv_smem + slot * Cfg::kKVTileBytes + p * Cfg::kKVPanelBytes, tm, kv_full + slot, p * 64,
+                      (t >> 1) * BN, h, b);
+        if (t == 0) load_q(1);
+      }
+    } else if (warp == 12 && lane == 0) {
+      // ============================================================= MMA issue
+      constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);                  // K-major operand (Q, K)
+      constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kKVPanelBytes, 1024);  // MN-major operand (V)
+      constexpr uint32_t kIdescQK = idesc_f16_f32(Cfg::BM, BN, false, false);
+      constexpr uint32_t kIdescPV = idesc_f16_f32(Cfg::BM, D, false, true);
+      const uint32_t q_addr = smem_u32(q_smem);
+      const uint32_t kv_addr = smem_u32(kv_smem);
+
+      auto issue_qk = [&](int i, int j) {  // S_i(j) = Q_i . K_j^T
+        const int t = 2 * j;
+        const int slot = t % STAGES;
+        mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x501, t);
+        tc_fence_after_sync();
+        const uint32_t qa = q_addr + i * Cfg::kQTileBytes;
+        const uint32_t ka = kv_addr + slot * Cfg::kKVTileBytes;
+        const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          mma_ss(t_s, smem_desc_at(kDescK, qa + (kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32),
+                 smem_desc_at(kDescK, ka + (kk >> 2) * Cfg::kKVPanelBytes + (kk & 3) * 32), kIdescQK, kk > 0);
+        }
+        mma_commit(s_full + i);
+        const bool last_user = (i == 1) || !(j < n_t[1]);
+        if (last_user) mma_commit(kv_empty + slot);
+      };
+      auto issue_pv = [&](int i, int j) {  // O_i (+)= P_i(j) . V_j
+        const int t = 2 * j + 1;
+        const int slot = t % STAGES;
+        mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x502, t);
+        mbar_wait(p_full + i, j & 1, abort_flag, 0x503 + i, j);
+        if (j > 0) mbar_wait(o_rescaled + i, (j - 1) & 1, abort_flag, 0x505 + i, j);
+        tc_fence_after_sync();
+        const uint32_t va = kv_addr + slot * Cfg::kKVTileBytes;
+        const uint32_t t_p = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
+        const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          mma_ts(t_o, t_p + kk * 8, smem_desc_at(kDescV, va + kk * 2048), kIdescPV, (j > 0 || kk > 0));
+        }
+        mma_commit(o_full + i);
+        const bool last_user = (i == 1) || !(j < n_t[1]);
+        if (last_user) mma_commit(kv_empty + slot);
+      };
+
+      for (int i = 0; i < 2; ++i) {
+        if (n_t[i] > 0) {
+          mbar_wait(q_full + i, 0, abort_flag, 0x511 + i);
+          issue_qk(i, 0);
+        }
+      }
+      for (int j = 0; j < n_max; ++j) {
+        for (int i = 0; i < 2; ++i) {
+          if (j < n_t[i]) {
+            issue_pv(i, j);
+            if (j + 1 < n_t[i]) issue_qk(i, j + 1);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+// Host launcher for the warp-specialised kernel. Returns an AttnReturnCode.
+template <int D, int BN, int STAGES>
+inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
+                              const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
+  using Cfg = WsCfg<D, BN, STAGES>;
+  CUtensorMap tm_q, tm_k, tm_v, tm_o;
+  int rc = make_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
+  if (rc != kAttnOk) return rc;
+  rc = make_attn_tensor_map(&tm_k, k, shp, st[1], BN);
+  if (rc != kAttnOk) return rc;
+  rc = make_attn_tensor_map(&tm_v, v, shp, st[2], BN);
+  if (rc != kAttnOk) return rc;
+  rc = make_attn_tensor_map(&tm_o, o, shp, st[3], Cfg::BM);
+  if (rc != kAttnOk) return rc;
+
+  auto kernel = attn_fwd_ws_kernel<D, BN, STAGES>;
+  static bool attr_done = false;  // one process drives one GPU: set once
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return kAttnSmemAttrFailed;
+    }
+    attr_done = true;
+  }
+  dim3 grid((shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM), shp.B * shp.H);
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,
+                                                           scale * 1.44269504088896340736f);
+  if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
+  return kAttnOk;
+}
+
+}  // namespace sm100
+}  // namespace fray

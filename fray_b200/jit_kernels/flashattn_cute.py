@@ -60,6 +60,7 @@ _RC_TENSOR_MAP = 6
 def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
     """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised), KV tile, KV stages."""
     space = [
+        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4},
         {"KIND": 0, "BLOCK_N": 128, "STAGES": 1},
         {"KIND": 0, "BLOCK_N": 64, "STAGES": 1},
     ]
