@@ -19,9 +19,10 @@ enum AttnKernelKind : int {
   kAttnWarpSpecialized = 1,  // two 128-row tiles per CTA, producer / MMA / softmax / correction roles
 };
 
-// KIND, D, BLOCK_N, STAGES are compile-time tuning keys; everything else is a run-time
-// argument. `rc` receives an AttnReturnCode; a non-zero value means nothing was launched.
-template <int KIND, int D, int BLOCK_N, int STAGES>
+// KIND, D, BLOCK_N, STAGES, POLY are compile-time tuning keys (POLY: how many of every four
+// element pairs evaluate exp2 by polynomial instead of the special-function unit; used by the
+// warp-specialised kernel only); everything else is a run-time argument. `rc` receives an AttnReturnCode; a non-zero value means nothing was launched.
+template <int KIND, int D, int BLOCK_N, int STAGES, int POLY = 0>
 inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, __half* o, int batch_size,
                              int num_heads, int seq_len, int q_sb, int q_sh, int q_ss, int k_sb, int k_sh, int k_ss,
                              int v_sb, int v_sh, int v_ss, int o_sb, int o_sh, int o_ss, bool causal, float scale,
@@ -34,7 +35,7 @@ inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, 
     rc = sm100::launch_attn_fwd_simple<D, BLOCK_N>(q, k, v, o, shp, st, causal, scale, stream);
   } else {
 #ifdef FRAY_HAS_WS_KERNEL
-    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES>(q, k, v, o, shp, st, causal, scale, stream);
+    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);
 #else
     static_assert(KIND == kAttnSimple, "warp-specialised kernel not available in this build");
 #endif

@@ -6,7 +6,7 @@
 //   warps 4-7   softmax group 1 (query tile 1)
 //   warps 8-11  correction group: rescales the O accumulators when a running max moved,
 //               and runs the epilogue (O/l -> fp16 -> shared memory -> TMA store)
-//   warp 12     MMA issue (one thread issues every tcgen05.mma / commit)
+//   warp 12     MMA issue for both tiles (warp-uniform code, one elected lane issues)
 //   warp 13     TMA producer (Q tiles once, then K_j, V_j through a ring of STAGES buffers)
 //   warps 14-15 idle (they only exist so that warps 12-15 form a full warpgroup for setmaxnreg)
 //
@@ -17,7 +17,8 @@
 //
 // Issue order in the MMA warp: S0(0) S1(0) | PV0(0) S0(1) PV1(0) S1(1) | PV0(1) S0(2) ...
 // so that while group 0 runs the softmax of S0(j+1) the tensor cores work on PV1(j) and
-// S1(j+1), and vice versa.
+// S1(j+1), and vice versa.  P.V is issued in four key chunks as the
+// softmax hands them over, so only the last quarter of it sits behind the softmax.
 //
 // Online softmax in base 2 with lazy rescaling: a tile's exponent offset m_ref only moves
 // when the running max grew by more than 2^8 in the scaled domain; until then P may exceed
@@ -39,6 +40,7 @@ struct WsCfg {
   static_assert(BN == 128, "the warp-specialised kernel uses 128-key tiles");
   static_assert(STAGES >= 2 && STAGES <= 8, "2..8 K/V buffers");
   static constexpr int BM = 128;               // rows per query tile
+  static constexpr int kPChunks = 4;           // P is handed to the MMA warp in this many column chunks
   static constexpr int kThreads = 512;
   static constexpr int kPanels = D / 64;       // 64-element (128-byte) column panels
   static constexpr int kQPanelBytes = BM * 128;
@@ -48,9 +50,14 @@ struct WsCfg {
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = 2 * kQTileBytes;
   static constexpr int kOffBars = kOffKV + STAGES * kKVTileBytes;
-  static constexpr int kNumBars = 2 + 2 * STAGES + 2 * 5;
+  static constexpr int kNumBars = 2 + 2 * STAGES + 2 * 4 + 2 * kPChunks;
   static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][128], l[2][128]
+#ifdef FRAY_ATTN_TRACE
+  static constexpr int kOffTrace = kOffStats + 4 * 128 * 4;
+  static constexpr int kSmemBytes = kOffTrace + 4 * 800 + 1024;
+#else
   static constexpr int kSmemBytes = kOffStats + 4 * 128 * 4 + 1024;                    // + alignment slack
+#endif
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of one CTA");
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
@@ -70,10 +77,35 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Optional role timeline for bring-up and tuning: with -DFRAY_ATTN_TRACE one thread per role of
+// CTA (0,0) stamps clock64 into a shared-memory table indexed by (event, tile, iteration < 40);
+// the table is copied to a device buffer at the end and read back with fray_attn_trace_read.
+// Compiled out by default.
+#ifndef FRAY_TRACE_ROW
+#define FRAY_TRACE_ROW 0  // which row's thread stamps the softmax events
+#endif
+#ifdef FRAY_ATTN_TRACE
+static constexpr int kTraceEvents = 10, kTraceIters = 40;
+static constexpr int kTraceWords = kTraceEvents * 2 * kTraceIters;
+__device__ unsigned int fray_attn_trace_buf[kTraceWords];
+#define FRAY_TRACE(event, tile, iter)                                                              \
+  do {                                                                                             \
+    if (trace_on && (iter) < kTraceIters)                                                          \
+      trace_sm[((event) * 2 + (tile)) * kTraceIters + (iter)] = static_cast<unsigned int>(clock64()); \
+  } while (0)
+inline int read_attn_trace(unsigned int* out, int max_words) {
+  const int n = max_words < kTraceWords ? max_words : kTraceWords;
+  if (cudaMemcpyFromSymbol(out, fray_attn_trace_buf, sizeof(unsigned int) * n) != cudaSuccess) return -1;
+  return n;
+}
+#else
+#define FRAY_TRACE(event, tile, iter) do { } while (0)
+#endif
+
 // Lazy-rescale threshold in the scaled base-2 domain: offsets move only when the max grew by > 2^8.
 static constexpr float kRescaleThreshold = 8.0f;
 
-template <int D, int BN, int STAGES>
+template <int D, int BN, int STAGES, int POLY>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -89,15 +121,19 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* kv_full = bars + 2;                 // [STAGES] producer -> MMA
   uint64_t* kv_empty = kv_full + STAGES;        // [STAGES] MMA -> producer
   uint64_t* s_full = kv_empty + STAGES;         // [2]   MMA -> softmax i        (S_i(j) complete)
-  uint64_t* p_full = s_full + 2;                // [2]   softmax i -> MMA        (P_i(j) stored)
-  uint64_t* o_full = p_full + 2;                // [2]   MMA -> correction       (PV_i(j) complete)
+  uint64_t* o_full = s_full + 2;                // [2]   MMA -> correction       (PV_i(j) complete)
   uint64_t* corr_ready = o_full + 2;            // [2]   softmax i -> correction (alpha_i(j) / final l published)
   uint64_t* o_rescaled = corr_ready + 2;        // [2]   correction -> MMA       (O_i ready for PV_i(j))
+  uint64_t* p_full = o_rescaled + 2;            // [2][kPChunks] softmax i -> MMA (chunk c of P_i(j) stored)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
   float* alpha_buf = reinterpret_cast<float*>(smem + Cfg::kOffStats);  // [2][128]
   float* l_buf = alpha_buf + 256;                                      // [2][128]
 
+#ifdef FRAY_ATTN_TRACE
+  unsigned int* trace_sm = reinterpret_cast<unsigned int*>(smem + Cfg::kOffTrace);
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0;
+#endif
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -109,28 +145,28 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   // Number of KV tiles each query tile consumes (0 = tile lies past the end of the sequence).
   const int n_kv = (seq_len + BN - 1) / BN;
-  int n_t[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  auto tiles_for = [&](int i) {
     const int row0 = m0 + i * Cfg::BM;
     int n = row0 < seq_len ? n_kv : 0;
     if (causal && n > 0) {
       const int lim = (row0 + Cfg::BM + BN - 1) / BN;
       n = lim < n ? lim : n;
     }
-    n_t[i] = n;
-  }
-  const int n_max = n_t[0] > n_t[1] ? n_t[0] : n_t[1];
+    return n;
+  };
+  const int n_t0 = tiles_for(0), n_t1 = tiles_for(1);  // scalars: an indexed array would live in local memory
+  const int n_max = n_t0 > n_t1 ? n_t0 : n_t1;
 
   if (tid == 0) {
+    FRAY_TRACE(6, 0, 0);  // CTA entry
     *abort_flag = (*reinterpret_cast<volatile int*>(&fray_attn_status[0]) != 0) ? 2u : 0u;
     for (int i = 0; i < 2; ++i) {
       mbar_init(q_full + i, 1);
       mbar_init(s_full + i, 1);
-      mbar_init(p_full + i, 128);
+      for (int c = 0; c < Cfg::kPChunks; ++c) mbar_init(p_full + i * Cfg::kPChunks + c, 4);  // one arrival per warp
       mbar_init(o_full + i, 1);
-      mbar_init(corr_ready + i, 128);
-      mbar_init(o_rescaled + i, 128);
+      mbar_init(corr_ready + i, 4);  // one arrival per warp: 32 lanes arriving on one barrier would serialise
+      mbar_init(o_rescaled + i, 4);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full + s, 1);
@@ -153,78 +189,180 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  if (tid == 0) FRAY_TRACE(6, 0, 1);  // set-up done
 
   if (warp < 8) {
     // =============================================================== softmax groups
     set_max_regs_inc<Cfg::kRegsSoftmax>();
     const int i = warp >> 2;              // query tile of this group
     const int r = tid & 127;              // row inside the tile
-    const int n_i = n_t[i];
+    const int n_i = i ? n_t1 : n_t0;
     const int row = m0 + i * Cfg::BM + r;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1) + lane_base;
     float m_ref = -INFINITY;  // exponent offset currently baked into P, l and O
     float l_run = 0.f;
 
+    constexpr int kChunkCols = BN / Cfg::kPChunks;  // 32 keys per chunk -> 16 packed fp16 columns
+    static_assert(Cfg::kPChunks == 4 && kChunkCols == 32, "the chunk schedule below is written for 4 x 32 keys");
+    uint64_t* p_bar = p_full + i * Cfg::kPChunks;
+
     for (int j = 0; j < n_i; ++j) {
       mbar_wait(s_full + i, j & 1, abort_flag, 0x201 + i, j);
       tc_fence_after_sync();
+      if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
       uint32_t sr[BN];
 #pragma unroll
       for (int c = 0; c < BN / 32; ++c) tmem_ld_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
       tmem_wait_ld();
+      if (r == FRAY_TRACE_ROW) FRAY_TRACE(1, i, j);
 
+      // The first tile and tiles that need masking settle the row max before any exponent is
+      // taken.  Every other tile speculates that the offset m_ref stays (it nearly always does
+      // under lazy rescaling): exponents of the first half start at once with the old offset
+      // while the max tree runs beside them on another pipe, and are redone only if the check fails.
       const int kv0 = j * BN;
-      if ((kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM))) {
-#pragma unroll
-        for (int c = 0; c < BN; ++c) {
-          const int kv = kv0 + c;
-          if (kv >= seq_len || (causal && kv > row)) sr[c] = __float_as_uint(-INFINITY);
-        }
-      }
+      const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+      const bool settle_first = (j == 0) || need_mask;
+      float alpha = 1.f;
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < BN; c += 4) {
-        mx0 = fmaxf(mx0, __uint_as_float(sr[c + 0]));
-        mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
-        mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
-      }
-      const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m_ref);
 
-      if (j == 0) {
-        m_ref = m_new;
-      } else {
-        float alpha = 1.f;
-        if ((m_new - m_ref) * scale_log2 > kRescaleThreshold) {
+      auto move_offset = [&](float m_new) {  // lazy rescale decision for this row
+        if (j == 0) {
+          m_ref = m_new;
+        } else if ((m_new - m_ref) * scale_log2 > kRescaleThreshold) {
           alpha = ex2_approx((m_ref - m_new) * scale_log2);
           l_run *= alpha;
           m_ref = m_new;
         }
-        alpha_buf[i * 128 + r] = alpha;
-        mbar_arrive(corr_ready + i);
-      }
-      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
+      };
 
-      float rs0 = 0.f, rs1 = 0.f;
+      if (settle_first) {
+        if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < BN; c += 2) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c]), scale_log2, neg_m));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c + 1]), scale_log2, neg_m));
-        rs0 += p0;
-        rs1 += p1;
-        sr[c >> 1] = pack_half2(p0, p1);
+          for (int c = 0; c < BN; ++c) {
+            const int kv = kv0 + c;
+            if (kv >= seq_len || (causal && kv > row)) sr[c] = __float_as_uint(-INFINITY);
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < BN; c += 8) {
+          mx0 = max3(mx0, __uint_as_float(sr[c + 0]), __uint_as_float(sr[c + 1]));
+          mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+          mx2 = max3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
+          mx3 = max3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
+        }
+        move_offset(fmaxf(max3(mx0, mx1, mx2), fmaxf(mx3, m_ref)));
       }
-      l_run += rs0 + rs1;
+      float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
+      const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+
+      // sr[q*32 .. q*32+31] <- exp2(S*c - m*c), in place.  WITH_MAX also folds those raw values and
+      // the matching ones of the second half into the max accumulators.
+      auto exp_chunk = [&](int q, bool with_max) {
+        const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
 #pragma unroll
-      for (int c = 0; c < BN / 64; ++c) tmem_st_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(p_full + i);
+        for (int c = 0; c < kChunkCols; c += 4) {
+          const int e = q * kChunkCols + c;
+          if (with_max) {
+            mx0 = max3(mx0, __uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
+            mx1 = max3(mx1, __uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3]));
+            mx2 = max3(mx2, __uint_as_float(sr[e + 64]), __uint_as_float(sr[e + 65]));
+            mx3 = max3(mx3, __uint_as_float(sr[e + 66]), __uint_as_float(sr[e + 67]));
+          }
+          float x0, x1, x2, x3;
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), scale2, negm2), x0, x1);
+          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3])), scale2, negm2), x2, x3);
+          // POLY of every 4 element pairs take the polynomial route, the rest the special-function unit.
+          float p0, p1, p2, p3;
+          if (((c >> 1) & 3) < POLY) {
+            ex2_poly_pair(x0, x1, p0, p1);
+          } else {
+            p0 = ex2_approx(x0);
+            p1 = ex2_approx(x1);
+          }
+          if ((((c >> 1) + 1) & 3) < POLY) {
+            ex2_poly_pair(x2, x3, p2, p3);
+          } else {
+            p2 = ex2_approx(x2);
+            p3 = ex2_approx(x3);
+          }
+          sr[e] = __float_as_uint(p0);
+          sr[e + 1] = __float_as_uint(p1);
+          sr[e + 2] = __float_as_uint(p2);
+          sr[e + 3] = __float_as_uint(p3);
+        }
+      };
+      uint64_t rs2a = pack_f32x2(0.f, 0.f), rs2b = rs2a;
+      // Round chunk q to fp16, add it to the row sum and store it to tensor memory.
+      auto store_chunk = [&](int q) {
+        uint32_t pk[kChunkCols / 2];
+#pragma unroll
+        for (int c = 0; c < kChunkCols; c += 4) {
+          const int e = q * kChunkCols + c;
+          const float p0 = __uint_as_float(sr[e]), p1 = __uint_as_float(sr[e + 1]);
+          const float p2 = __uint_as_float(sr[e + 2]), p3 = __uint_as_float(sr[e + 3]);
+          rs2a = add_f32x2(rs2a, pack_f32x2(p0, p1));
+          rs2b = add_f32x2(rs2b, pack_f32x2(p2, p3));
+          pk[c >> 1] = pack_half2(p0, p1);
+          pk[(c >> 1) + 1] = pack_half2(p2, p3);
+        }
+        tmem_st_x16(t_s + q * (kChunkCols / 2), pk);
+      };
+      // The store of chunk q has landed: let the MMA warp start on it.
+      auto publish_chunk = [&](int q) {
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_bar + q);
+      };
+
+      exp_chunk(0, !settle_first);
+      exp_chunk(1, !settle_first);
+      if (!settle_first) {
+        const float m_old = m_ref;
+        move_offset(fmaxf(max3(mx0, mx1, mx2), fmaxf(mx3, m_ref)));
+        if (__any_sync(0xffffffffu, m_ref != m_old)) {
+          // Speculation failed somewhere in this warp: fetch the first half of S again and redo it
+          // (rows whose offset did not move simply recompute the same values).
+          neg_m = -m_ref * scale_log2;
+          tmem_ld_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
+          tmem_ld_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
+          tmem_wait_ld();
+          exp_chunk(0, false);
+          exp_chunk(1, false);
+        }
+      }
+      if (j > 0) {
+        alpha_buf[i * 128 + r] = alpha;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(corr_ready + i);
+      }
+      if (r == FRAY_TRACE_ROW) FRAY_TRACE(2, i, j);
+
+      // Exponents of the next chunk are issued before the previous chunk's hand-over so the
+      // special-function pipe never drains while a store is being waited for.
+      store_chunk(0);
+      exp_chunk(2, false);
+      publish_chunk(0);
+      if (r == FRAY_TRACE_ROW) FRAY_TRACE(9, i, j);
+      store_chunk(1);
+      exp_chunk(3, false);
+      publish_chunk(1);
+      store_chunk(2);
+      publish_chunk(2);
+      store_chunk(3);
+      publish_chunk(3);
+      if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
+      float ra0, ra1, rb0, rb1;
+      unpack_f32x2(rs2a, ra0, ra1);
+      unpack_f32x2(rs2b, rb0, rb1);
+      l_run += (ra0 + ra1) + (rb0 + rb1);
     }
     if (n_i > 0) {
       l_buf[i * 128 + r] = l_run;
-      mbar_arrive(corr_ready + i);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(corr_ready + i);
     }
   } else if (warp < 12) {
     // =============================================================== correction group + epilogue
@@ -234,7 +372,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     for (int j = 1; j < n_max; ++j) {
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        if (j < n_t[i]) {
+        if (j < (i ? n_t1 : n_t0)) {
           const uint32_t ph = (j - 1) & 1;
           mbar_wait(corr_ready + i, ph, abort_flag, 0x301 + i, j);
           const float alpha = alpha_buf[i * 128 + r];
@@ -254,14 +392,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             tmem_wait_st();
             tc_fence_before_sync();
           }
-          mbar_arrive(o_rescaled + i);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(o_rescaled + i);
         }
       }
     }
     // Epilogue: O_i / l_i -> fp16 -> shared memory (the dead Q_i buffer, 128B-swizzled) -> TMA store.
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      const int n_i = n_t[i];
+      const int n_i = i ? n_t1 : n_t0;
       if (n_i > 0) {
         const uint32_t ph = (n_i - 1) & 1;
         mbar_wait(corr_ready + i, ph, abort_flag, 0x321 + i, n_i);
@@ -269,6 +408,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const float inv_l = l > 0.f ? 1.f / l : 1.f;
         mbar_wait(o_full + i, ph, abort_flag, 0x331 + i, n_i);
         tc_fence_after_sync();
+        if (r == 0) FRAY_TRACE(6, 1, i);  // last P.V of tile i complete, epilogue starts
         const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1) + lane_base;
         uint8_t* o_tile = q_smem + i * Cfg::kQTileBytes;
 #pragma unroll
@@ -298,13 +438,17 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
     }
-    if (r == 0) tma_store_wait_all();
+    if (r == 0) {
+      FRAY_TRACE(6, 1, 2);  // stores issued
+      tma_store_wait_all();
+      FRAY_TRACE(6, 1, 3);  // stores complete
+    }
   } else {
     set_max_regs_dec<Cfg::kRegsOther>();
     if (warp == 13 && lane == 0) {
       // ============================================================= TMA producer
       auto load_q = [&](int i) {
-        if (n_t[i] > 0) {
+        if ((i ? n_t1 : n_t0) > 0) {
           mbar_expect_tx(q_full + i, Cfg::kQTileBytes);
 #pragma unroll
           for (int p = 0; p < Cfg::kPanels; ++p)
@@ -325,63 +469,79 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                       (t >> 1) * BN, h, b);
         if (t == 0) load_q(1);
       }
-    } else if (warp == 12 && lane == 0) {
-      // ============================================================= MMA issue
+    } else if (warp == 12) {
+      // ============================================================= MMA issue (whole warp, one elected lane issues)
+      // One warp serves both tiles in a fixed alternation.  That ordering is what keeps the two
+      // tiles in anti-phase (one in its softmax while the other owns the tensor pipe); two
+      // independent issuing warps were measured to drift into lock-step and lose the overlap.
       constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);                  // K-major operand (Q, K)
       constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kKVPanelBytes, 1024);  // MN-major operand (V)
       constexpr uint32_t kIdescQK = idesc_f16_f32(Cfg::BM, BN, false, false);
       constexpr uint32_t kIdescPV = idesc_f16_f32(Cfg::BM, D, false, true);
       const uint32_t q_addr = smem_u32(q_smem);
       const uint32_t kv_addr = smem_u32(kv_smem);
+      const int n0 = n_t0, n1 = n_t1;
 
       auto issue_qk = [&](int i, int j) {  // S_i(j) = Q_i . K_j^T
         const int t = 2 * j;
         const int slot = t % STAGES;
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x501, t);
         tc_fence_after_sync();
-        const uint32_t qa = q_addr + i * Cfg::kQTileBytes;
-        const uint32_t ka = kv_addr + slot * Cfg::kKVTileBytes;
+        const uint64_t qd = smem_desc_at(kDescK, q_addr + i * Cfg::kQTileBytes);
+        const uint64_t kd = smem_desc_at(kDescK, kv_addr + slot * Cfg::kKVTileBytes);
         const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          mma_ss(t_s, smem_desc_at(kDescK, qa + (kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32),
-                 smem_desc_at(kDescK, ka + (kk >> 2) * Cfg::kKVPanelBytes + (kk & 3) * 32), kIdescQK, kk > 0);
+          // descriptor start addresses are in 16-byte units
+          const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
+          const uint32_t koff = ((kk >> 2) * Cfg::kKVPanelBytes + (kk & 3) * 32) >> 4;
+          mma_ss_elect(t_s, qd + qoff, kd + koff, kIdescQK, kk > 0);
         }
-        mma_commit(s_full + i);
-        const bool last_user = (i == 1) || !(j < n_t[1]);
-        if (last_user) mma_commit(kv_empty + slot);
+        mma_commit_elect(s_full + i);
+        if ((i == 1) || !(j < n1)) mma_commit_elect(kv_empty + slot);
+        FRAY_TRACE(8, i, j);
       };
-      auto issue_pv = [&](int i, int j) {  // O_i (+)= P_i(j) . V_j
+      auto issue_pv = [&](int i, int j) {  // O_i (+)= P_i(j) . V_j, chunk by chunk as P arrives
         const int t = 2 * j + 1;
         const int slot = t % STAGES;
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x502, t);
-        mbar_wait(p_full + i, j & 1, abort_flag, 0x503 + i, j);
         if (j > 0) mbar_wait(o_rescaled + i, (j - 1) & 1, abort_flag, 0x505 + i, j);
-        tc_fence_after_sync();
-        const uint32_t va = kv_addr + slot * Cfg::kKVTileBytes;
+        const uint64_t vd = smem_desc_at(kDescV, kv_addr + slot * Cfg::kKVTileBytes);
         const uint32_t t_p = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
         const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
+        constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          mma_ts(t_o, t_p + kk * 8, smem_desc_at(kDescV, va + kk * 2048), kIdescPV, (j > 0 || kk > 0));
+        for (int q = 0; q < Cfg::kPChunks; ++q) {
+          mbar_wait(p_full + i * Cfg::kPChunks + q, j & 1, abort_flag, 0x503 + i, j);
+          tc_fence_after_sync();
+          if (q == 0) FRAY_TRACE(5, i, j);
+#pragma unroll
+          for (int s2 = 0; s2 < kStepsPerChunk; ++s2) {
+            const int kk = q * kStepsPerChunk + s2;
+            mma_ts_elect(t_o, t_p + kk * 8, vd + ((kk * 2048) >> 4), kIdescPV, (j > 0 || kk > 0));
+          }
         }
-        mma_commit(o_full + i);
-        const bool last_user = (i == 1) || !(j < n_t[1]);
-        if (last_user) mma_commit(kv_empty + slot);
+        mma_commit_elect(o_full + i);
+        if ((i == 1) || !(j < n1)) mma_commit_elect(kv_empty + slot);
+        FRAY_TRACE(7, i, j);
       };
 
-      for (int i = 0; i < 2; ++i) {
-        if (n_t[i] > 0) {
-          mbar_wait(q_full + i, 0, abort_flag, 0x511 + i);
-          issue_qk(i, 0);
-        }
+      if (n0 > 0) {
+        mbar_wait(q_full + 0, 0, abort_flag, 0x511);
+        issue_qk(0, 0);
+      }
+      if (n1 > 0) {
+        mbar_wait(q_full + 1, 0, abort_flag, 0x512);
+        issue_qk(1, 0);
       }
       for (int j = 0; j < n_max; ++j) {
-        for (int i = 0; i < 2; ++i) {
-          if (j < n_t[i]) {
-            issue_pv(i, j);
-            if (j + 1 < n_t[i]) issue_qk(i, j + 1);
-          }
+        if (j < n0) {
+          issue_pv(0, j);
+          if (j + 1 < n0) issue_qk(0, j + 1);
+        }
+        if (j < n1) {
+          issue_pv(1, j);
+          if (j + 1 < n1) issue_qk(1, j + 1);
         }
       }
     }
@@ -390,10 +550,16 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+#ifdef FRAY_ATTN_TRACE
+  if (tid == 0) FRAY_TRACE(6, 0, 2);  // CTA exit
+  __syncthreads();
+  if (trace_on)
+    for (int w = tid; w < kTraceWords; w += Cfg::kThreads) fray_attn_trace_buf[w] = trace_sm[w];
+#endif
 }
 
 // Host launcher for the warp-specialised kernel. Returns an AttnReturnCode.
-template <int D, int BN, int STAGES>
+template <int D, int BN, int STAGES, int POLY>
 inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
                               const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
   using Cfg = WsCfg<D, BN, STAGES>;
@@ -407,7 +573,8 @@ inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v,
   rc = make_attn_tensor_map(&tm_o, o, shp, st[3], Cfg::BM);
   if (rc != kAttnOk) return rc;
 
-  auto kernel = attn_fwd_ws_kernel<D, BN, STAGES>;
+  static_assert(POLY >= 0 && POLY <= 4, "POLY counts polynomial pairs out of every 4");
+  auto kernel = attn_fwd_ws_kernel<D, BN, STAGES, POLY>;
   static bool attr_done = false;  // one process drives one GPU: set once
   if (!attr_done) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {

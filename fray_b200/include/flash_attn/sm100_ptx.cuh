@@ -192,6 +192,47 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Warp-collective forms: the whole warp executes the call with uniform operands and one
+// elected lane issues the instruction.  Keeping the issuing code warp-uniform lets the
+// compiler hold descriptors in uniform registers, which makes back-to-back MMA issue several
+// times faster than issuing from a single-lane branch.  elect.sync picks the same lane for
+// the same member mask every time, so commits track the MMAs issued through these calls.
+__device__ __forceinline__ void mma_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, e;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, e;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n"
+      ".reg .pred e;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(smem_u32(bar))
+      : "memory");
+}
+
 // Arrives once on `bar` when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -269,6 +310,50 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// Two-lane packed fp32 arithmetic (one issue slot for two elements).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// 2^x for two values on the FMA/ALU pipes instead of the special-function unit: round x to the
+// nearest integer n with the 1.5*2^23 trick, evaluate a cubic for 2^(x-n) on [-0.5, 0.5]
+// (max relative error 7.5e-5, below fp16 rounding) and add n to the exponent field.
+// Inputs are clamped at -120 so the exponent arithmetic cannot wrap (-inf included).
+__device__ __forceinline__ void ex2_poly_pair(float x0, float x1, float& p0, float& p1) {
+  x0 = fmaxf(x0, -120.f);
+  x1 = fmaxf(x1, -120.f);
+  const uint64_t x2 = pack_f32x2(x0, x1);
+  const uint64_t t2 = add_f32x2(x2, pack_f32x2(12582912.f, 12582912.f));
+  const uint64_t n2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.f, -1.f), x2);
+  uint64_t q2 = fma_f32x2(pack_f32x2(0.0551716685f, 0.0551716685f), f2, pack_f32x2(0.2426111251f, 0.2426111251f));
+  q2 = fma_f32x2(q2, f2, pack_f32x2(0.6932609677f, 0.6932609677f));
+  q2 = fma_f32x2(q2, f2, pack_f32x2(0.9999280572f, 0.9999280572f));
+  float t0, t1, q0, q1;
+  unpack_f32x2(t2, t0, t1);
+  unpack_f32x2(q2, q0, q1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   uint32_t r;

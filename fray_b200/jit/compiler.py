@@ -123,11 +123,14 @@ def put(path: str, data, is_binary: bool = False) -> None:
 
 
 def get_nvcc_flags() -> Tuple[str, ...]:
-    ptxas = "--ptxas-options=--register-usage-level=10" + (",--verbose" if "FRAY_PTXAS_VERBOSE" in os.environ else "")
+    # No --register-usage-level override: the reference's level 10 trades instruction-level
+    # parallelism for registers, which the warp-specialised kernel budgets itself (setmaxnreg).
+    ptxas = "--ptxas-options=--warn-on-spills" + (",--verbose" if "FRAY_PTXAS_VERBOSE" in os.environ else "")
+    extra = tuple(os.getenv("FRAY_NVCC_EXTRA_FLAGS", "").split())  # e.g. -DFRAY_ATTN_TRACE (part of the cache key)
     return (
         "-std=c++17", "-O3", "--expt-relaxed-constexpr", "--expt-extended-lambda", "-lineinfo",
         _ARCH_FLAG, "-shared", ptxas, "--diag-suppress=177,174,940",
-        "--compiler-options=-fPIC,-O3,-Wno-deprecated-declarations,-Wno-abi",
+        "--compiler-options=-fPIC,-O3,-Wno-deprecated-declarations,-Wno-abi", *extra,
     )
 
 

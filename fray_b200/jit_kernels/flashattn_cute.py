@@ -20,7 +20,7 @@ includes = ('"flash_attn/flash_attn_sm100.cuh"',)
 
 template = """
 // Templated args from Python JIT call
-fray::flash_attn_sm100<{KIND}, {D}, {BLOCK_N}, {STAGES}>(
+fray::flash_attn_sm100<{KIND}, {D}, {BLOCK_N}, {STAGES}, {POLY}>(
     Q, K, V, O, batch_size, num_heads, seq_len,
     q_stride_b, q_stride_h, q_stride_s, k_stride_b, k_stride_h, k_stride_s,
     v_stride_b, v_stride_h, v_stride_s, o_stride_b, o_stride_h, o_stride_s,
@@ -33,8 +33,13 @@ extern "C" EXPORT_API int fray_attn_status(int* out4, int clear) {
     return fray::read_attn_status(out4, clear != 0);
 }
 extern "C" EXPORT_API void fray_attn_kernel_info(int* out4) {
-    out4[0] = {KIND}; out4[1] = {D}; out4[2] = {BLOCK_N}; out4[3] = {STAGES};
+    out4[0] = {KIND}; out4[1] = {D}; out4[2] = {BLOCK_N}; out4[3] = {STAGES} + 16 * {POLY};
 }
+#ifdef FRAY_ATTN_TRACE
+extern "C" EXPORT_API int fray_attn_trace_read(unsigned int* out, int max_words) {
+    return fray::sm100::read_attn_trace(out, max_words);
+}
+#endif
 """
 
 _STRIDE_NAMES = tuple(f"{t}_stride_{d}" for t in "qkvo" for d in "bhs")
@@ -60,13 +65,16 @@ _RC_TENSOR_MAP = 6
 def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
     """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised), KV tile, KV stages."""
     space = [
-        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4},
-        {"KIND": 0, "BLOCK_N": 128, "STAGES": 1},
-        {"KIND": 0, "BLOCK_N": 64, "STAGES": 1},
+        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},
+        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},
+        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 2},
+        {"KIND": 0, "BLOCK_N": 128, "STAGES": 1, "POLY": 0},
+        {"KIND": 0, "BLOCK_N": 64, "STAGES": 1, "POLY": 0},
     ]
     forced = os.getenv("FRAY_ATTN_FORCE")  # e.g. "KIND=0,BLOCK_N=64,STAGES=1"
     if forced:
-        point = {kv.split("=")[0].strip(): int(kv.split("=")[1]) for kv in forced.split(",")}
+        point = {"POLY": 0}
+        point.update({kv.split("=")[0].strip(): int(kv.split("=")[1]) for kv in forced.split(",")})
         return (point,)
     return tuple(space)
 
