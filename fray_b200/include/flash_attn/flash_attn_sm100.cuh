@@ -21,7 +21,8 @@ enum AttnKernelKind : int {
 
 // KIND, D, BLOCK_N, STAGES, POLY are compile-time tuning keys (POLY: how many of every four
 // element pairs evaluate exp2 by polynomial instead of the special-function unit; used by the
-// warp-specialised kernel only); everything else is a run-time argument. `rc` receives an AttnReturnCode; a non-zero value means nothing was launched.
+// warp-specialised kernel only); everything else is a run-time argument.  `rc` receives an
+// AttnReturnCode; a non-zero value means nothing was launched.
 template <int KIND, int D, int BLOCK_N, int STAGES, int POLY = 0>
 inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, __half* o, int batch_size,
                              int num_heads, int seq_len, int q_sb, int q_sh, int q_ss, int k_sb, int k_sh, int k_ss,

@@ -154,7 +154,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
     return n;
   };
-  const int n_t0 = tiles_for(0), n_t1 = tiles_for(1);  // scalars: an indexed array would live in local memory
+#ifdef FRAY_DEBUG_SINGLE_TILE
+  const int n_t0 = tiles_for(0), n_t1 = 0;  // timing experiment: tile 1 idle (its output rows are not computed)
+#else
+  const int n_t0 = tiles_for(0), n_t1 = tiles_for(1);
+#endif  // scalars: an indexed array would live in local memory
   const int n_max = n_t0 > n_t1 ? n_t0 : n_t1;
 
   if (tid == 0) {
@@ -211,153 +215,119 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_wait(s_full + i, j & 1, abort_flag, 0x201 + i, j);
       tc_fence_after_sync();
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
-      uint32_t sr[BN];
-#pragma unroll
-      for (int c = 0; c < BN / 32; ++c) tmem_ld_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
-      tmem_wait_ld();
-      if (r == FRAY_TRACE_ROW) FRAY_TRACE(1, i, j);
 
-      // The first tile and tiles that need masking settle the row max before any exponent is
-      // taken.  Every other tile speculates that the offset m_ref stays (it nearly always does
-      // under lazy rescaling): exponents of the first half start at once with the old offset
-      // while the max tree runs beside them on another pipe, and are redone only if the check fails.
+      // Register diet: the row is handled as two 64-key halves.  Both are loaded once for the row
+      // max; only the first stays in registers for its exponentials, and the second is fetched from
+      // tensor memory again afterwards (a ~100-cycle load) instead of being held.  With 128 live
+      // score registers the scheduler had too little room to overlap the dependent FFMA -> MUFU ->
+      // FADD/convert chains and the loop ran well below the special-function unit's rate.
       const int kv0 = j * BN;
       const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
-      const bool settle_first = (j == 0) || need_mask;
-      float alpha = 1.f;
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      auto load_half = [&](uint32_t (&h)[64], int half) {
+        tmem_ld_x32(t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(h[0]));
+        tmem_ld_x32(t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(h[32]));
+      };
+      auto mask_half = [&](uint32_t (&h)[64], int half) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int kv = kv0 + half * 64 + c;
+          if (kv >= seq_len || (causal && kv > row)) h[c] = __float_as_uint(-INFINITY);
+        }
+      };
 
-      auto move_offset = [&](float m_new) {  // lazy rescale decision for this row
-        if (j == 0) {
-          m_ref = m_new;
-        } else if ((m_new - m_ref) * scale_log2 > kRescaleThreshold) {
+      uint32_t sa[64];
+      float mx[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) mx[q] = -INFINITY;
+      {
+        uint32_t sb[64];
+        load_half(sa, 0);
+        load_half(sb, 1);
+        tmem_wait_ld();
+        if (r == FRAY_TRACE_ROW) FRAY_TRACE(1, i, j);
+        if (need_mask) {
+          mask_half(sa, 0);
+          mask_half(sb, 1);
+        }
+#pragma unroll
+        for (int c = 0; c < 64; c += 8) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) mx[q] = fmaxf(mx[q], fmaxf(__uint_as_float(sa[c + q]), __uint_as_float(sb[c + q])));
+        }
+      }
+      const float m_new = fmaxf(fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                      fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))), m_ref);
+      // Lazy rescale: the offset only moves when the max grew by more than the threshold.
+      if (j == 0) {
+        m_ref = m_new;
+      } else {
+        float alpha = 1.f;
+        if ((m_new - m_ref) * scale_log2 > kRescaleThreshold) {
           alpha = ex2_approx((m_ref - m_new) * scale_log2);
           l_run *= alpha;
           m_ref = m_new;
         }
-      };
-
-      if (settle_first) {
-        if (need_mask) {
-#pragma unroll
-          for (int c = 0; c < BN; ++c) {
-            const int kv = kv0 + c;
-            if (kv >= seq_len || (causal && kv > row)) sr[c] = __float_as_uint(-INFINITY);
-          }
-        }
-#pragma unroll
-        for (int c = 0; c < BN; c += 8) {
-          mx0 = max3(mx0, __uint_as_float(sr[c + 0]), __uint_as_float(sr[c + 1]));
-          mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
-          mx2 = max3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
-          mx3 = max3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
-        }
-        move_offset(fmaxf(max3(mx0, mx1, mx2), fmaxf(mx3, m_ref)));
+        alpha_buf[i * 128 + r] = alpha;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(corr_ready + i);
       }
-      float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
-      const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
+      if (r == FRAY_TRACE_ROW) FRAY_TRACE(2, i, j);
 
-      // sr[q*32 .. q*32+31] <- exp2(S*c - m*c), in place.  WITH_MAX also folds those raw values and
-      // the matching ones of the second half into the max accumulators.
-      auto exp_chunk = [&](int q, bool with_max) {
-        const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
+      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+      // h[...] <- exp2(S*c - m*c) for one 64-key half, in place.  POLY of every 4 element pairs take
+      // the polynomial route, the rest the special-function unit.
+      auto exp_half = [&](uint32_t (&h)[64]) {
 #pragma unroll
-        for (int c = 0; c < kChunkCols; c += 4) {
-          const int e = q * kChunkCols + c;
-          if (with_max) {
-            mx0 = max3(mx0, __uint_as_float(sr[e]), __uint_as_float(sr[e + 1]));
-            mx1 = max3(mx1, __uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3]));
-            mx2 = max3(mx2, __uint_as_float(sr[e + 64]), __uint_as_float(sr[e + 65]));
-            mx3 = max3(mx3, __uint_as_float(sr[e + 66]), __uint_as_float(sr[e + 67]));
-          }
-          float x0, x1, x2, x3;
-          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[e]), __uint_as_float(sr[e + 1])), scale2, negm2), x0, x1);
-          unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sr[e + 2]), __uint_as_float(sr[e + 3])), scale2, negm2), x2, x3);
-          // POLY of every 4 element pairs take the polynomial route, the rest the special-function unit.
-          float p0, p1, p2, p3;
+        for (int c = 0; c < 64; c += 2) {
+          const float x0 = fmaf(__uint_as_float(h[c]), scale_log2, neg_m);
+          const float x1 = fmaf(__uint_as_float(h[c + 1]), scale_log2, neg_m);
+          float p0, p1;
           if (((c >> 1) & 3) < POLY) {
             ex2_poly_pair(x0, x1, p0, p1);
           } else {
             p0 = ex2_approx(x0);
             p1 = ex2_approx(x1);
           }
-          if ((((c >> 1) + 1) & 3) < POLY) {
-            ex2_poly_pair(x2, x3, p2, p3);
-          } else {
-            p2 = ex2_approx(x2);
-            p3 = ex2_approx(x3);
-          }
-          sr[e] = __float_as_uint(p0);
-          sr[e + 1] = __float_as_uint(p1);
-          sr[e + 2] = __float_as_uint(p2);
-          sr[e + 3] = __float_as_uint(p3);
+          h[c] = __float_as_uint(p0);
+          h[c + 1] = __float_as_uint(p1);
         }
       };
-      uint64_t rs2a = pack_f32x2(0.f, 0.f), rs2b = rs2a;
-      // Round chunk q to fp16, add it to the row sum and store it to tensor memory.
-      auto store_chunk = [&](int q) {
+      // Round 32 keys to fp16, add them to the row sum, store them to tensor memory as chunk q and
+      // hand the chunk to the MMA warp once the store has landed.
+      auto store_publish = [&](const uint32_t (&h)[64], int off, int q) {
         uint32_t pk[kChunkCols / 2];
 #pragma unroll
         for (int c = 0; c < kChunkCols; c += 4) {
-          const int e = q * kChunkCols + c;
-          const float p0 = __uint_as_float(sr[e]), p1 = __uint_as_float(sr[e + 1]);
-          const float p2 = __uint_as_float(sr[e + 2]), p3 = __uint_as_float(sr[e + 3]);
-          rs2a = add_f32x2(rs2a, pack_f32x2(p0, p1));
-          rs2b = add_f32x2(rs2b, pack_f32x2(p2, p3));
+          const float p0 = __uint_as_float(h[off + c]), p1 = __uint_as_float(h[off + c + 1]);
+          const float p2 = __uint_as_float(h[off + c + 2]), p3 = __uint_as_float(h[off + c + 3]);
+          rs0 += p0;
+          rs1 += p1;
+          rs2 += p2;
+          rs3 += p3;
           pk[c >> 1] = pack_half2(p0, p1);
           pk[(c >> 1) + 1] = pack_half2(p2, p3);
         }
         tmem_st_x16(t_s + q * (kChunkCols / 2), pk);
-      };
-      // The store of chunk q has landed: let the MMA warp start on it.
-      auto publish_chunk = [&](int q) {
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_bar + q);
       };
 
-      exp_chunk(0, !settle_first);
-      exp_chunk(1, !settle_first);
-      if (!settle_first) {
-        const float m_old = m_ref;
-        move_offset(fmaxf(max3(mx0, mx1, mx2), fmaxf(mx3, m_ref)));
-        if (__any_sync(0xffffffffu, m_ref != m_old)) {
-          // Speculation failed somewhere in this warp: fetch the first half of S again and redo it
-          // (rows whose offset did not move simply recompute the same values).
-          neg_m = -m_ref * scale_log2;
-          tmem_ld_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
-          tmem_ld_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
-          tmem_wait_ld();
-          exp_chunk(0, false);
-          exp_chunk(1, false);
-        }
-      }
-      if (j > 0) {
-        alpha_buf[i * 128 + r] = alpha;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(corr_ready + i);
-      }
-      if (r == FRAY_TRACE_ROW) FRAY_TRACE(2, i, j);
-
-      // Exponents of the next chunk are issued before the previous chunk's hand-over so the
-      // special-function pipe never drains while a store is being waited for.
-      store_chunk(0);
-      exp_chunk(2, false);
-      publish_chunk(0);
+      exp_half(sa);
+      uint32_t sb2[64];
+      load_half(sb2, 1);  // second half again; it sits at columns [64,128), clear of the P chunks below
+      store_publish(sa, 0, 0);
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(9, i, j);
-      store_chunk(1);
-      exp_chunk(3, false);
-      publish_chunk(1);
-      store_chunk(2);
-      publish_chunk(2);
-      store_chunk(3);
-      publish_chunk(3);
+      store_publish(sa, 32, 1);
+      tmem_wait_ld();
+      if (need_mask) mask_half(sb2, 1);
+      exp_half(sb2);
+      store_publish(sb2, 0, 2);
+      store_publish(sb2, 32, 3);
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
-      float ra0, ra1, rb0, rb1;
-      unpack_f32x2(rs2a, ra0, ra1);
-      unpack_f32x2(rs2b, rb0, rb1);
-      l_run += (ra0 + ra1) + (rb0 + rb1);
+      l_run += (rs0 + rs1) + (rs2 + rs3);
     }
     if (n_i > 0) {
       l_buf[i * 128 + r] = l_run;

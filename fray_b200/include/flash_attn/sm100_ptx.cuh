@@ -339,21 +339,18 @@ __device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
 // nearest integer n with the 1.5*2^23 trick, evaluate a cubic for 2^(x-n) on [-0.5, 0.5]
 // (max relative error 7.5e-5, below fp16 rounding) and add n to the exponent field.
 // Inputs are clamped at -120 so the exponent arithmetic cannot wrap (-inf included).
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -120.f);
+  const float t = x + 12582912.f;          // low mantissa bits now hold round(x)
+  const float f = x - (t - 12582912.f);    // in [-0.5, 0.5]
+  float q = fmaf(0.0551716685f, f, 0.2426111251f);
+  q = fmaf(q, f, 0.6932609677f);
+  q = fmaf(q, f, 0.9999280572f);
+  return __uint_as_float(__float_as_uint(q) + (__float_as_uint(t) << 23));
+}
 __device__ __forceinline__ void ex2_poly_pair(float x0, float x1, float& p0, float& p1) {
-  x0 = fmaxf(x0, -120.f);
-  x1 = fmaxf(x1, -120.f);
-  const uint64_t x2 = pack_f32x2(x0, x1);
-  const uint64_t t2 = add_f32x2(x2, pack_f32x2(12582912.f, 12582912.f));
-  const uint64_t n2 = add_f32x2(t2, pack_f32x2(-12582912.f, -12582912.f));
-  const uint64_t f2 = fma_f32x2(n2, pack_f32x2(-1.f, -1.f), x2);
-  uint64_t q2 = fma_f32x2(pack_f32x2(0.0551716685f, 0.0551716685f), f2, pack_f32x2(0.2426111251f, 0.2426111251f));
-  q2 = fma_f32x2(q2, f2, pack_f32x2(0.6932609677f, 0.6932609677f));
-  q2 = fma_f32x2(q2, f2, pack_f32x2(0.9999280572f, 0.9999280572f));
-  float t0, t1, q0, q1;
-  unpack_f32x2(t2, t0, t1);
-  unpack_f32x2(q2, q0, q1);
-  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+  p0 = ex2_poly(x0);
+  p1 = ex2_poly(x1);
 }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   uint32_t r;

@@ -67,7 +67,6 @@ def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
     space = [
         {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},
         {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},
-        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 2},
         {"KIND": 0, "BLOCK_N": 128, "STAGES": 1, "POLY": 0},
         {"KIND": 0, "BLOCK_N": 64, "STAGES": 1, "POLY": 0},
     ]

@@ -44,8 +44,8 @@ void launch(void* Q, void* K, void* V, void* O, int batch_size, int num_heads, i
  * (fray/jit_kernels/tuner.py:45-50 only sees the always-zero return code). */
 int fray_attn_status(int* out4, int clear);
 
-/* out4 = {kernel kind, head dim D, KV tile length, KV pipeline stages} this library was
- * instantiated with - the template keys the reference keeps only in the source text
+/* out4 = {kernel kind, head dim D, KV tile length, KV pipeline stages + 16 * polynomial-exp2
+ * share} this library was instantiated with - the template keys the reference keeps only in the source text
  * (fray/jit_kernels/flashattn_cute.py:32-38). */
 void fray_attn_kernel_info(int* out4);
 

@@ -29,7 +29,7 @@ def test_arg_table_matches_template():
     assert names[-3:] == ["causal", "scale", "stream"]
     for n in names:
         assert n in op.template
-    for key in ("{KIND}", "{D}", "{BLOCK_N}", "{STAGES}"):
+    for key in ("{KIND}", "{D}", "{BLOCK_N}", "{STAGES}", "{POLY}"):
         assert key in op.template
 
 
@@ -43,7 +43,9 @@ def test_usable_strides():
 
 def test_forced_space(monkeypatch):
     monkeypatch.setenv("FRAY_ATTN_FORCE", "KIND=0, BLOCK_N=64, STAGES=1")
-    assert op.tuning_space(128) == ({"KIND": 0, "BLOCK_N": 64, "STAGES": 1},)
+    assert op.tuning_space(128) == ({"POLY": 0, "KIND": 0, "BLOCK_N": 64, "STAGES": 1},)
+    monkeypatch.setenv("FRAY_ATTN_FORCE", "KIND=1,BLOCK_N=128,STAGES=4,POLY=1")
+    assert op.tuning_space(128) == ({"POLY": 1, "KIND": 1, "BLOCK_N": 128, "STAGES": 4},)
 
 
 class FakeRuntime:
