@@ -29,6 +29,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 NOMINAL_FP16_TFLOPS = 2250.0
+# DRAM traffic of the warp-specialised kernel from one ncu capture of the `small` workload
+# (32 (b,h) units of S=4096, D=128, non-causal): dram__bytes_read.sum + dram__bytes_write.sum.
+# Units are independent, so a launch with more units of the same shape moves proportionally more.
+NCU_DRAM_BYTES_PER_UNIT_S4096_D128 = (100.783360e6 + 14.093824e6) / 32
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
 WORKLOADS = {
@@ -127,6 +131,10 @@ def cpu_attention_sample(B, H, S, D, causal, budget_s=12.0):
     budget is used; returns (TFLOP/s, units done, seconds, threads)."""
     import torch.nn.functional as F
     from oracle import attention_ref as ref
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, RuntimeError):
+        pass
     threads = torch.get_num_threads()
     q, k, v = ref.make_slice(5, 0, S, D)
     q, k, v = (t.float().reshape(1, 1, S, D) for t in (q, k, v))
@@ -145,6 +153,11 @@ def run_reference(args, B, H, S, D, causal, rank):
         return
     import torch.nn.functional as F
     from oracle import attention_ref as ref
+    # torchrun pins OMP_NUM_THREADS=1; the CPU arm is meant to use every core this process may run on
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, RuntimeError):
+        pass
     threads = torch.get_num_threads()
     units_per_step = 2
     q, k, v = ref.make_inputs(5, range(units_per_step)) if (B, H, S, D) == (4, 32, 4096, 128) else tuple(
@@ -278,7 +291,13 @@ def main():
         value = flops * world / (ms_step * 1e-3) / 1e12
         per_gpu = value / world
         e2e_value = flops * world / (e2e_ms_step * 1e-3) / 1e12
-        peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        # burst GEMM figure when the timed region ran unthrottled, sustained one when the power cap was seen
+        capped = bool(clocks and "sw_power_cap" in (clocks.get("reasons") or []))
+        peak_key = "bf16_tflops_sustained" if capped else "bf16_tflops"
+        peak = float(peaks.get(peak_key, FALLBACK_PEAKS[peak_key]))
+        traffic = None
+        if (S, D, causal) == (4096, 128, False):
+            traffic = NCU_DRAM_BYTES_PER_UNIT_S4096_D128 * B * H
         tuned = {str(sig[1]): keys for sig, keys in jit_tuner.tuned_keys.items()}
         line = {
             "metric": "flash_attn_fwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
@@ -289,10 +308,14 @@ def main():
                        if B * H * S * D * 8 > 126e6 else "inputs smaller than L2, no flush",
                        "kernel": tuned},
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
-                         "frac": per_gpu / peak, "traffic": None,
-                         "peak_source": f"{peak_src} sustained bf16 GEMM (steps run back to back)",
+                         "frac": per_gpu / peak, "traffic": traffic,
+                         "traffic_note": "bytes per launch per GPU, ncu capture of the one-batch case scaled by units",
+                         "algorithmic_bytes": 4 * B * H * S * D * 2,
+                         "peak_source": f"{peak_src} {'sustained' if capped else 'burst'} bf16 GEMM "
+                                        f"({'power cap seen' if capped else 'no throttle reason'} during the timed region)",
                          "frac_of_nominal_2250": per_gpu / NOMINAL_FP16_TFLOPS,
-                         "frac_of_burst": per_gpu / float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))},
+                         "frac_of_sustained_gemm": per_gpu / float(peaks.get("bf16_tflops_sustained",
+                                                                         FALLBACK_PEAKS["bf16_tflops_sustained"]))},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms_step,
                     "h2d_bytes_per_step": 3 * q.numel() * 2 * world, "d2h_bytes_per_step": out.numel() * 2 * world},
             "gpu_launches": args.steps * world,

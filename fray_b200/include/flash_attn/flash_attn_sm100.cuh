@@ -6,10 +6,8 @@
 
 #include "fwd_simple_sm100.cuh"
 #include "host_sm100.cuh"
-#if __has_include("fwd_ws_sm100.cuh")
 #include "fwd_ws_sm100.cuh"
-#define FRAY_HAS_WS_KERNEL 1
-#endif
+#include "fwd_wsp_sm100.cuh"
 
 namespace fray {
 
@@ -17,6 +15,7 @@ namespace fray {
 enum AttnKernelKind : int {
   kAttnSimple = 0,  // one 128-row tile per CTA, single role, no overlap
   kAttnWarpSpecialized = 1,  // two 128-row tiles per CTA, producer / MMA / softmax / correction roles
+  kAttnPersistent = 2,       // the same roles in one CTA per SM that loops over work items
 };
 
 // KIND, D, BLOCK_N, STAGES, POLY are compile-time tuning keys (POLY: how many of every four
@@ -34,12 +33,11 @@ inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, 
   if (rc != kAttnOk) return;
   if constexpr (KIND == kAttnSimple) {
     rc = sm100::launch_attn_fwd_simple<D, BLOCK_N>(q, k, v, o, shp, st, causal, scale, stream);
-  } else {
-#ifdef FRAY_HAS_WS_KERNEL
+  } else if constexpr (KIND == kAttnWarpSpecialized) {
     rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);
-#else
-    static_assert(KIND == kAttnSimple, "warp-specialised kernel not available in this build");
-#endif
+  } else {
+    static_assert(KIND == kAttnPersistent, "unknown kernel kind");
+    rc = sm100::launch_attn_fwd_wsp<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);
   }
 }
 

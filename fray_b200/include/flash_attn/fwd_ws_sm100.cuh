@@ -30,6 +30,7 @@
 
 #include "host_sm100.cuh"
 #include "sm100_ptx.cuh"
+#include "softmax_tile_sm100.cuh"
 
 namespace fray {
 namespace sm100 {
@@ -50,7 +51,7 @@ struct WsCfg {
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = 2 * kQTileBytes;
   static constexpr int kOffBars = kOffKV + STAGES * kKVTileBytes;
-  static constexpr int kNumBars = 2 + 2 * STAGES + 2 * 4 + 2 * kPChunks;
+  static constexpr int kNumBars = 2 + 2 * STAGES + 2 * 5 + 2 * kPChunks;
   static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][128], l[2][128]
 #ifdef FRAY_ATTN_TRACE
   static constexpr int kOffTrace = kOffStats + 4 * 128 * 4;
@@ -65,17 +66,6 @@ struct WsCfg {
   static constexpr int kRegsSoftmax = 184, kRegsCorrection = 80, kRegsOther = 64;
 };
 
-template <int N>
-__device__ __forceinline__ void set_max_regs_inc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void set_max_regs_dec() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
 
 // Optional role timeline for bring-up and tuning: with -DFRAY_ATTN_TRACE one thread per role of
 // CTA (0,0) stamps clock64 into a shared-memory table indexed by (event, tile, iteration < 40);
@@ -102,8 +92,6 @@ inline int read_attn_trace(unsigned int* out, int max_words) {
 #define FRAY_TRACE(event, tile, iter) do { } while (0)
 #endif
 
-// Lazy-rescale threshold in the scaled base-2 domain: offsets move only when the max grew by > 2^8.
-static constexpr float kRescaleThreshold = 8.0f;
 
 template <int D, int BN, int STAGES, int POLY>
 __global__ void __launch_bounds__(512, 1)
@@ -125,6 +113,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   uint64_t* corr_ready = o_full + 2;            // [2]   softmax i -> correction (alpha_i(j) / final l published)
   uint64_t* o_rescaled = corr_ready + 2;        // [2]   correction -> MMA       (O_i ready for PV_i(j))
   uint64_t* p_full = o_rescaled + 2;            // [2][kPChunks] softmax i -> MMA (chunk c of P_i(j) stored)
+  uint64_t* sfu_turn = p_full + 2 * Cfg::kPChunks;  // [2] softmax (1-i) -> softmax i: the special-function unit is yours
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
   float* alpha_buf = reinterpret_cast<float*>(smem + Cfg::kOffStats);  // [2][128]
@@ -171,6 +160,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(o_full + i, 1);
       mbar_init(corr_ready + i, 4);  // one arrival per warp: 32 lanes arriving on one barrier would serialise
       mbar_init(o_rescaled + i, 4);
+      mbar_init(sfu_turn + i, 4);
     }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full + s, 1);
@@ -201,14 +191,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const int i = warp >> 2;              // query tile of this group
     const int r = tid & 127;              // row inside the tile
     const int n_i = i ? n_t1 : n_t0;
+    const int n_both = n_t0 < n_t1 ? n_t0 : n_t1;  // KV steps that both tiles run
     const int row = m0 + i * Cfg::BM + r;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1) + lane_base;
     float m_ref = -INFINITY;  // exponent offset currently baked into P, l and O
     float l_run = 0.f;
 
-    constexpr int kChunkCols = BN / Cfg::kPChunks;  // 32 keys per chunk -> 16 packed fp16 columns
-    static_assert(Cfg::kPChunks == 4 && kChunkCols == 32, "the chunk schedule below is written for 4 x 32 keys");
+    static_assert(Cfg::kPChunks == kSoftmaxPChunks, "softmax_tile hands P over in kSoftmaxPChunks chunks");
     uint64_t* p_bar = p_full + i * Cfg::kPChunks;
 
     for (int j = 0; j < n_i; ++j) {
@@ -216,118 +206,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_after_sync();
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
 
-      // Register diet: the row is handled as two 64-key halves.  Both are loaded once for the row
-      // max; only the first stays in registers for its exponentials, and the second is fetched from
-      // tensor memory again afterwards (a ~100-cycle load) instead of being held.  With 128 live
-      // score registers the scheduler had too little room to overlap the dependent FFMA -> MUFU ->
-      // FADD/convert chains and the loop ran well below the special-function unit's rate.
       const int kv0 = j * BN;
       const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
-      auto load_half = [&](uint32_t (&h)[64], int half) {
-        tmem_ld_x32(t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(h[0]));
-        tmem_ld_x32(t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(h[32]));
-      };
-      auto mask_half = [&](uint32_t (&h)[64], int half) {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          const int kv = kv0 + half * 64 + c;
-          if (kv >= seq_len || (causal && kv > row)) h[c] = __float_as_uint(-INFINITY);
-        }
-      };
-
-      uint32_t sa[64];
-      float mx[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) mx[q] = -INFINITY;
-      {
-        uint32_t sb[64];
-        load_half(sa, 0);
-        load_half(sb, 1);
-        tmem_wait_ld();
-        if (r == FRAY_TRACE_ROW) FRAY_TRACE(1, i, j);
-        if (need_mask) {
-          mask_half(sa, 0);
-          mask_half(sb, 1);
-        }
-#pragma unroll
-        for (int c = 0; c < 64; c += 8) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) mx[q] = fmaxf(mx[q], fmaxf(__uint_as_float(sa[c + q]), __uint_as_float(sb[c + q])));
-        }
-      }
-      const float m_new = fmaxf(fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                                      fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))), m_ref);
-      // Lazy rescale: the offset only moves when the max grew by more than the threshold.
-      if (j == 0) {
-        m_ref = m_new;
-      } else {
-        float alpha = 1.f;
-        if ((m_new - m_ref) * scale_log2 > kRescaleThreshold) {
-          alpha = ex2_approx((m_ref - m_new) * scale_log2);
-          l_run *= alpha;
-          m_ref = m_new;
-        }
-        alpha_buf[i * 128 + r] = alpha;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(corr_ready + i);
-      }
-      const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
-      if (r == FRAY_TRACE_ROW) FRAY_TRACE(2, i, j);
-
-      float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
-      // h[...] <- exp2(S*c - m*c) for one 64-key half, in place.  POLY of every 4 element pairs take
-      // the polynomial route, the rest the special-function unit.
-      auto exp_half = [&](uint32_t (&h)[64]) {
-#pragma unroll
-        for (int c = 0; c < 64; c += 2) {
-          const float x0 = fmaf(__uint_as_float(h[c]), scale_log2, neg_m);
-          const float x1 = fmaf(__uint_as_float(h[c + 1]), scale_log2, neg_m);
-          float p0, p1;
-          if (((c >> 1) & 3) < POLY) {
-            ex2_poly_pair(x0, x1, p0, p1);
-          } else {
-            p0 = ex2_approx(x0);
-            p1 = ex2_approx(x1);
-          }
-          h[c] = __float_as_uint(p0);
-          h[c + 1] = __float_as_uint(p1);
-        }
-      };
-      // Round 32 keys to fp16, add them to the row sum, store them to tensor memory as chunk q and
-      // hand the chunk to the MMA warp once the store has landed.
-      auto store_publish = [&](const uint32_t (&h)[64], int off, int q) {
-        uint32_t pk[kChunkCols / 2];
-#pragma unroll
-        for (int c = 0; c < kChunkCols; c += 4) {
-          const float p0 = __uint_as_float(h[off + c]), p1 = __uint_as_float(h[off + c + 1]);
-          const float p2 = __uint_as_float(h[off + c + 2]), p3 = __uint_as_float(h[off + c + 3]);
-          rs0 += p0;
-          rs1 += p1;
-          rs2 += p2;
-          rs3 += p3;
-          pk[c >> 1] = pack_half2(p0, p1);
-          pk[(c >> 1) + 1] = pack_half2(p2, p3);
-        }
-        tmem_st_x16(t_s + q * (kChunkCols / 2), pk);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(p_bar + q);
-      };
-
-      exp_half(sa);
-      uint32_t sb2[64];
-      load_half(sb2, 1);  // second half again; it sits at columns [64,128), clear of the P chunks below
-      store_publish(sa, 0, 0);
-      if (r == FRAY_TRACE_ROW) FRAY_TRACE(9, i, j);
-      store_publish(sa, 32, 1);
-      tmem_wait_ld();
-      if (need_mask) mask_half(sb2, 1);
-      exp_half(sb2);
-      store_publish(sb2, 0, 2);
-      store_publish(sb2, 32, 3);
+      // Steps both tiles run take turns on the special-function unit; tile 0 goes first (its first
+      // wait uses the parity of the phase "before" the barrier's first one, which reads as complete).
+      const bool take_turns = j < n_both;
+      softmax_tile<BN, POLY>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, need_mask, kv0, row, seq_len,
+                             causal, scale_log2, lane, m_ref, l_run, take_turns ? sfu_turn + i : nullptr,
+                             take_turns ? sfu_turn + (1 - i) : nullptr, (j + 1 - i) & 1, abort_flag);
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
-      l_run += (rs0 + rs1) + (rs2 + rs3);
     }
     if (n_i > 0) {
       l_buf[i * 128 + r] = l_run;
@@ -417,7 +304,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     set_max_regs_dec<Cfg::kRegsOther>();
     if (warp == 13 && lane == 0) {
       // ============================================================= TMA producer
-      auto load_q = [&](int i) {
+      auto load_q = [&](int i) __attribute__((always_inline)) {
         if ((i ? n_t1 : n_t0) > 0) {
           mbar_expect_tx(q_full + i, Cfg::kQTileBytes);
 #pragma unroll
@@ -452,7 +339,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const uint32_t kv_addr = smem_u32(kv_smem);
       const int n0 = n_t0, n1 = n_t1;
 
-      auto issue_qk = [&](int i, int j) {  // S_i(j) = Q_i . K_j^T
+      auto issue_qk = [&](int i, int j) __attribute__((always_inline)) {  // S_i(j) = Q_i . K_j^T
         const int t = 2 * j;
         const int slot = t % STAGES;
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x501, t);
@@ -471,7 +358,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if ((i == 1) || !(j < n1)) mma_commit_elect(kv_empty + slot);
         FRAY_TRACE(8, i, j);
       };
-      auto issue_pv = [&](int i, int j) {  // O_i (+)= P_i(j) . V_j, chunk by chunk as P arrives
+      auto issue_pv = [&](int i, int j) __attribute__((always_inline)) {  // O_i (+)= P_i(j) . V_j, chunk by chunk as P arrives
         const int t = 2 * j + 1;
         const int slot = t % STAGES;
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x502, t);

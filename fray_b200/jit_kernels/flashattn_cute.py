@@ -63,8 +63,9 @@ _RC_TENSOR_MAP = 6
 
 
 def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
-    """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised), KV tile, KV stages."""
+    """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised, 2 persistent), KV tile, KV stages, exp2 mix."""
     space = [
+        {"KIND": 2, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},
         {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},
         {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},
         {"KIND": 0, "BLOCK_N": 128, "STAGES": 1, "POLY": 0},
