@@ -17,7 +17,8 @@
 //
 // Issue order in the MMA warp: S0(0) S1(0) | PV0(0) S0(1) PV1(0) S1(1) | PV0(1) S0(2) ...
 // so that while group 0 runs the softmax of S0(j+1) the tensor cores work on PV1(j) and
-// S1(j+1), and vice versa.  P.V is issued in four key chunks as the
+// S1(j+1), and vice versa.  (One issuing warp per tile and turn-taking of the softmax groups on
+// the special-function unit were both measured slower than this fixed alternation.)  P.V is issued in four key chunks as the
 // softmax hands them over, so only the last quarter of it sits behind the softmax.
 //
 // Online softmax in base 2 with lazy rescaling: a tile's exponent offset m_ref only moves
@@ -202,7 +203,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint64_t* p_bar = p_full + i * Cfg::kPChunks;
 
     for (int j = 0; j < n_i; ++j) {
-      mbar_wait(s_full + i, j & 1, abort_flag, 0x201 + i, j);
+      FRAY_CRIT_WAIT(s_full + i, j & 1, abort_flag, 0x201 + i, j);
       tc_fence_after_sync();
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
 
@@ -210,7 +211,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
       // Steps both tiles run take turns on the special-function unit; tile 0 goes first (its first
       // wait uses the parity of the phase "before" the barrier's first one, which reads as complete).
-      const bool take_turns = j < n_both;
+      const bool take_turns = kSfuTurns && j < n_both;
       softmax_tile<BN, POLY>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, need_mask, kv0, row, seq_len,
                              causal, scale_log2, lane, m_ref, l_run, take_turns ? sfu_turn + i : nullptr,
                              take_turns ? sfu_turn + (1 - i) : nullptr, (j + 1 - i) & 1, abort_flag);
@@ -369,7 +370,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
 #pragma unroll
         for (int q = 0; q < Cfg::kPChunks; ++q) {
-          mbar_wait(p_full + i * Cfg::kPChunks + q, j & 1, abort_flag, 0x503 + i, j);
+          FRAY_CRIT_WAIT(p_full + i * Cfg::kPChunks + q, j & 1, abort_flag, 0x503 + i, j);
           tc_fence_after_sync();
           if (q == 0) FRAY_TRACE(5, i, j);
 #pragma unroll

@@ -66,6 +66,12 @@ struct WspCfg {
   static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 65536, "register budgets exceed the file");
 };
 
+// Compile-time tile index handed to the generic role lambdas.
+template <int I>
+struct TileTag {
+  static constexpr int value = I;
+};
+
 // Work item -> coordinates.  Items are numbered (batch*head)-major; within a head the pair index
 // runs from the heaviest causal pair down.
 struct WspItem {
@@ -192,14 +198,14 @@ attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       float m_ref = -INFINITY;
       float l_run = 0.f;
       for (int j = 0; j < n_i; ++j) {
-        mbar_wait(s_full + i, s_count & 1, abort_flag, 0x601 + i, j);
+        FRAY_CRIT_WAIT(s_full + i, s_count & 1, abort_flag, 0x601 + i, j);
         if (r == 0) FRAY_TRACE(0, i, s_count);
         ++s_count;
         tc_fence_after_sync();
         const int kv0 = j * BN;
         const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > row0));
         // Steps both tiles run take turns on the special-function unit, tile 0 first.
-        const bool take_turns = j < (w.n0 < w.n1 ? w.n0 : w.n1);
+        const bool take_turns = kSfuTurns && j < (w.n0 < w.n1 ? w.n0 : w.n1);
         softmax_tile<BN, POLY>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, need_mask, kv0, row,
                                seq_len, causal, scale_log2, lane, m_ref, l_run, take_turns ? sfu_turn + i : nullptr,
                                take_turns ? sfu_turn + (1 - i) : nullptr, (turn_count + 1 - i) & 1, abort_flag);
@@ -342,81 +348,91 @@ attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
     } else if (warp == 12) {
       // ============================================================= MMA issue (whole warp, one elected lane issues)
+      // One warp serves both tiles in a fixed alternation (tile 0's step, tile 1's step, ...): that
+      // ordering is what keeps the tiles half a step apart, one in its softmax while the other owns
+      // the tensor pipe.  Per tile the order is K/V ring order - entry K_j: S_i(j) = Q_i.K_j^T, entry
+      // V_j: O_i += P_i(j).V_j - and it carries over from one item to the next, so a tile's first
+      // Q.K^T of the next item follows its last P.V directly.
       constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);
       constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kKVPanelBytes, 1024);
       constexpr uint32_t kIdescQK = idesc_f16_f32(Cfg::BM, BN, false, false);
       constexpr uint32_t kIdescPV = idesc_f16_f32(Cfg::BM, D, false, true);
+      constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
       const uint32_t q_addr = smem_u32(q_smem);
       const uint32_t kv_addr = smem_u32(kv_smem);
-      uint32_t t_base = 0;               // ring index of the current item's K_0
-      // per-tile counters as scalars (an indexed array would live in local memory)
-      uint32_t q_count0 = 0, q_count1 = 0;        // q_full phases consumed
-      uint32_t pv_count0 = 0, pv_count1 = 0;      // P.V steps issued (phase of the p_full chunks)
-      uint32_t resc_count0 = 0, resc_count1 = 0;  // o_rescaled phases consumed
-      uint32_t items_done0 = 0, items_done1 = 0;  // items finished per tile (phase of o_free)
-      bool prefetched0 = false, prefetched1 = false;
-      uint32_t qk_issued0 = 0, qk_issued1 = 0;  // Q.K^T batches issued per tile (trace index only)
 
-      // S_i = Q_i . K^T with K in ring entry `t`; `last_user` releases the entry, `last_qk` the Q buffer.
-      auto issue_qk = [&](int i, uint32_t t, bool last_user, bool last_qk) __attribute__((always_inline)) {
+      // Per-tile progress.  Every field is only touched through a compile-time tile index, so the
+      // two instances stay in registers.
+      struct TileState {
+        uint32_t q_count = 0;     // q_full phases consumed
+        uint32_t pv_count = 0;    // P.V steps issued (phase of the p_full chunks)
+        uint32_t resc_count = 0;  // o_rescaled phases consumed
+        uint32_t items_done = 0;  // items finished (phase of o_free)
+        uint32_t qk_trace = 0;    // Q.K^T batches issued (timeline index only)
+      };
+      TileState st0, st1;
+
+      // S_i = Q_i . K^T with K in ring entry t.  new_q: first use of a freshly loaded Q tile;
+      // last_user releases the ring entry, last_qk the Q buffer.
+      auto issue_qk = [&](auto tile, TileState& st, uint32_t t, bool new_q, bool last_user, bool last_qk)
+          __attribute__((always_inline)) {
+        constexpr int i = decltype(tile)::value;
         const int slot = t % STAGES;
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x901, t);
+        if (new_q) {
+          mbar_wait(q_full + i, st.q_count & 1, abort_flag, 0x911 + i, t);
+          ++st.q_count;
+        }
         tc_fence_after_sync();
         const uint64_t qd = smem_desc_at(kDescK, q_addr + i * Cfg::kQTileBytes);
         const uint64_t kd = smem_desc_at(kDescK, kv_addr + slot * Cfg::kKVTileBytes);
-        const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
+        constexpr uint32_t t_s_off = (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
           const uint32_t koff = ((kk >> 2) * Cfg::kKVPanelBytes + (kk & 3) * 32) >> 4;
-          mma_ss_elect(t_s, qd + qoff, kd + koff, kIdescQK, kk > 0);
+          mma_ss_elect(tmem_base + t_s_off, qd + qoff, kd + koff, kIdescQK, kk > 0);
         }
         mma_commit_elect(s_full + i);
         if (last_user) mma_commit_elect(kv_empty + slot);
         if (last_qk) mma_commit_elect(q_empty + i);
-        FRAY_TRACE(8, i, (i ? qk_issued1 : qk_issued0));
-        ++(i ? qk_issued1 : qk_issued0);
+        FRAY_TRACE(8, i, st.qk_trace);
+        ++st.qk_trace;
       };
-      // O_i (+)= P_i . V with V in ring entry `t`, chunk by chunk as P arrives.
-      auto issue_pv = [&](int i, int j, uint32_t t, bool last_user) __attribute__((always_inline)) {
+      // O_i (+)= P_i . V with V in ring entry t, chunk by chunk as P arrives.
+      auto issue_pv = [&](auto tile, TileState& st, int j, uint32_t t, bool last_user) __attribute__((always_inline)) {
+        constexpr int i = decltype(tile)::value;
         const int slot = t % STAGES;
-        uint32_t& resc_count = i ? resc_count1 : resc_count0;
-        uint32_t& pv_count = i ? pv_count1 : pv_count0;
-        const uint32_t items_done = i ? items_done1 : items_done0;
-        FRAY_TRACE(1, i, pv_count);  // P.V step entered
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x902, t);
-        FRAY_TRACE(2, i, pv_count);  // V tile present
         if (j > 0) {
-          mbar_wait(o_rescaled + i, resc_count & 1, abort_flag, 0x905 + i, j);
-          ++resc_count;
-        } else if (items_done > 0) {
-          mbar_wait(o_free + i, (items_done - 1) & 1, abort_flag, 0x907 + i, j);
+          mbar_wait(o_rescaled + i, st.resc_count & 1, abort_flag, 0x905 + i, j);
+          ++st.resc_count;
+        } else if (st.items_done > 0) {
+          mbar_wait(o_free + i, (st.items_done - 1) & 1, abort_flag, 0x907 + i, j);
         }
-        FRAY_TRACE(3, i, pv_count);  // O ready
         const uint64_t vd = smem_desc_at(kDescV, kv_addr + slot * Cfg::kKVTileBytes);
-        const uint32_t t_p = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
-        const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
-        constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
+        constexpr uint32_t t_p_off = (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
+        constexpr uint32_t t_o_off = (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
 #pragma unroll
         for (int q = 0; q < Cfg::kPChunks; ++q) {
-          mbar_wait(p_full + i * Cfg::kPChunks + q, pv_count & 1, abort_flag, 0x903 + i, j);
+          FRAY_CRIT_WAIT(p_full + i * Cfg::kPChunks + q, st.pv_count & 1, abort_flag, 0x903 + i, j);
           tc_fence_after_sync();
-          if (q == 0) FRAY_TRACE(5, i, pv_count);
+          if (q == 0) FRAY_TRACE(5, i, st.pv_count);
 #pragma unroll
           for (int s2 = 0; s2 < kStepsPerChunk; ++s2) {
             const int kk = q * kStepsPerChunk + s2;
-            mma_ts_elect(t_o, t_p + kk * 8, vd + ((kk * 2048) >> 4), kIdescPV, (j > 0 || kk > 0));
+            mma_ts_elect(tmem_base + t_o_off, tmem_base + t_p_off + kk * 8, vd + ((kk * 2048) >> 4), kIdescPV,
+                         (j > 0 || kk > 0));
           }
         }
-        FRAY_TRACE(7, i, pv_count);
-        ++pv_count;
+        FRAY_TRACE(7, i, st.pv_count);
+        ++st.pv_count;
         mma_commit_elect(o_full + i);
         if (last_user) mma_commit_elect(kv_empty + slot);
       };
 
-      // One pass of the loop body per (KV step, tile); j = -1 is the item's lead-in, where only a
-      // first Q.K^T may be due.  Each of issue_pv / issue_qk has a single call site so that the
-      // warp's instruction footprint stays small (the roles of a CTA share the instruction cache).
+      uint32_t t_base = 0;  // ring index of the current item's K_0
+      bool started0 = false, started1 = false;  // the item's first Q.K^T was issued from the previous item's tail
       for (int item = first_item; item < n_items; item += item_step) {
         const WspItem w = wsp_decode_item<Cfg::BM, BN>(item, n_pairs, num_heads, seq_len, causal);
         const bool has_next = item + item_step < n_items;
@@ -424,51 +440,33 @@ attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (has_next) nx = wsp_decode_item<Cfg::BM, BN>(item + item_step, n_pairs, num_heads, seq_len, causal);
         const uint32_t t_next = t_base + 2 * w.n_max;  // ring index of the next item's K_0
 
-        for (int j = -1; j < w.n_max; ++j) {
-#pragma unroll 1
-          for (int i = 0; i < 2; ++i) {
-            const int n_i = i ? w.n1 : w.n0;
-            if (n_i == 0) continue;
-            uint32_t& q_count = i ? q_count1 : q_count0;
-            bool& prefetched = i ? prefetched1 : prefetched0;
-            if (j >= 0 && j < n_i) issue_pv(i, j, t_base + 2 * j + 1, (i == 1) || !(j < w.n1));
-
-            // Which Q.K^T, if any, follows for this tile?
-            bool do_qk = false, new_q = false, last_user = false, last_qk = false;
-            uint32_t t_k = 0;
-            if (j + 1 < n_i) {
-              if (j >= 0) {
-                do_qk = true;  // next KV step of this item
-              } else if (!prefetched) {
-                do_qk = true;  // first step, not started from the previous item's tail
-                new_q = true;
-              }
-              t_k = t_base + 2 * (j + 1);
-              last_user = (i == 1) || !(j + 1 < w.n1);
-              last_qk = (j + 2 == n_i);
-              if (j < 0) prefetched = false;
-            } else if (j + 1 == n_i) {
-              // Tile i has finished this item.  Start it on the next item right away when the ring
-              // can hold that item's K_0 beside everything the other tile still needs.
-              ++(i ? items_done1 : items_done0);
-              const int nn_i = i ? nx.n1 : nx.n0;
-              if (has_next && nn_i > 0 && 2 * (w.n_max - n_i) + 2 <= STAGES) {
-                do_qk = true;
-                new_q = true;
-                t_k = t_next;
-                last_user = (i == 1) || !(0 < nx.n1);
-                last_qk = (nn_i == 1);
-                prefetched = true;
-              }
+        // One tile's share of KV step j (j = -1: the item's lead-in, where only a first Q.K^T may be due).
+        auto tile_step = [&](auto tile, TileState& st, bool& started, int j) __attribute__((always_inline)) {
+          constexpr int i = decltype(tile)::value;
+          const int n_i = i ? w.n1 : w.n0;
+          if (n_i == 0) return;
+          if (j >= 0 && j < n_i) issue_pv(tile, st, j, t_base + 2 * j + 1, (i == 1) || !(j < w.n1));
+          if (j + 1 < n_i) {
+            if (j >= 0) {
+              issue_qk(tile, st, t_base + 2 * (j + 1), false, (i == 1) || !(j + 1 < w.n1), j + 2 == n_i);
+            } else {
+              if (!started) issue_qk(tile, st, t_base, true, (i == 1) || !(0 < w.n1), n_i == 1);
+              started = false;
             }
-            if (do_qk) {
-              if (new_q) {
-                mbar_wait(q_full + i, q_count & 1, abort_flag, 0x911 + i, item);
-                ++q_count;
-              }
-              issue_qk(i, t_k, last_user, last_qk);
+          } else if (j + 1 == n_i) {
+            // Tile i has finished this item.  Start it on the next item right away when the ring can
+            // hold that item's K_0 beside everything the other tile still needs.
+            ++st.items_done;
+            const int nn_i = i ? nx.n1 : nx.n0;
+            if (has_next && nn_i > 0 && 2 * (w.n_max - n_i) + 2 <= STAGES) {
+              issue_qk(tile, st, t_next, true, (i == 1) || !(0 < nx.n1), nn_i == 1);
+              started = true;
             }
           }
+        };
+        for (int j = -1; j < w.n_max; ++j) {
+          tile_step(TileTag<0>{}, st0, started0, j);
+          tile_step(TileTag<1>{}, st1, started1, j);
         }
         t_base = t_next;
       }

@@ -91,6 +91,39 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Same contract as mbar_wait, but polls with the non-blocking test_wait instead of the suspending
+// try_wait.  A suspended waiter was measured to resume a few hundred cycles after the barrier
+// flips; on the hand-overs that sit on the critical path (scores ready, probabilities ready) a
+// polling waiter reacts within a shared-memory round trip at the price of a few issue slots.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               uint32_t site, uint32_t extra = 0) {
+  if (mbar_test_wait(bar, parity)) return;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (!mbar_test_wait(bar, parity)) {
+    if ((++polls & 255u) == 0u) {
+      if (*abort_flag) return;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        report_timeout(abort_flag, site, extra);
+        return;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

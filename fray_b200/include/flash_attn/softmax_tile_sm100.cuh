@@ -25,6 +25,20 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Waits on the critical path poll (mbar_wait_spin); -DFRAY_SUSPENDING_WAITS switches them back to
+// the suspending form for comparison.
+#ifdef FRAY_SUSPENDING_WAITS
+#define FRAY_CRIT_WAIT mbar_wait
+#else
+#define FRAY_CRIT_WAIT mbar_wait_spin
+#endif
+
+// Whether the two softmax groups take turns on the special-function unit (-DFRAY_SFU_TURNS=0/1).
+#ifndef FRAY_SFU_TURNS
+#define FRAY_SFU_TURNS 0  // measured slower than letting the groups overlap freely
+#endif
+static constexpr bool kSfuTurns = FRAY_SFU_TURNS != 0;
+
 // Lazy-rescale threshold in the scaled base-2 domain: offsets move only when the max grew by > 2^8.
 static constexpr float kRescaleThreshold = 8.0f;
 // P is handed to the MMA warp in this many column chunks (one mbarrier each, one arrival per warp).
@@ -147,7 +161,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
 
   uint32_t sb2[64];
   load_half(sb2, 1);  // second half again; it sits at columns [64,128), clear of the P chunks below
-  if (my_turn != nullptr) mbar_wait(my_turn, turn_parity, abort_flag, 0xA01, kv0);
+  if (my_turn != nullptr) FRAY_CRIT_WAIT(my_turn, turn_parity, abort_flag, 0xA01, kv0);
   exp_half(sa);
   store_publish(sa, 0, 0);
   store_publish(sa, 32, 1);
