@@ -102,6 +102,117 @@ __device__ __forceinline__ WspItem wsp_decode_item(int item, int n_pairs, int nu
   return w;
 }
 
+
+// ---- MMA-issue helpers of the persistent kernel.  Free functions with scalar reference parameters
+// (rather than lambdas over a state struct) so that the per-tile counters stay in registers: the
+// issuing warp is a serial resource and every local-memory round trip in it idles the tensor pipe.
+struct WspMmaCtx {
+  uint64_t* kv_full;
+  uint64_t* kv_empty;
+  uint64_t* q_full;
+  uint64_t* q_empty;
+  uint64_t* s_full;
+  uint64_t* o_full;
+  uint64_t* o_rescaled;
+  uint64_t* o_free;
+  uint64_t* p_full;
+  volatile uint32_t* abort_flag;
+  uint32_t q_addr, kv_addr, tmem_base;
+};
+
+// S_i = Q_i . K^T with K in ring entry t.  new_q: first use of a freshly loaded Q tile; last_user
+// releases the ring entry, last_qk the Q buffer.
+template <class Cfg, int D, int BN, int STAGES, int I>
+__device__ __forceinline__ void wsp_issue_qk(const WspMmaCtx& c, uint32_t t, bool new_q, bool last_user, bool last_qk,
+                                             uint32_t& q_count) {
+  constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);
+  constexpr uint32_t kIdescQK = idesc_f16_f32(Cfg::BM, BN, false, false);
+  const int slot = t % STAGES;
+  mbar_wait(c.kv_full + slot, (t / STAGES) & 1, c.abort_flag, 0x901, t);
+  if (new_q) {
+    mbar_wait(c.q_full + I, q_count & 1, c.abort_flag, 0x911 + I, t);
+    ++q_count;
+  }
+  tc_fence_after_sync();
+  const uint64_t qd = smem_desc_at(kDescK, c.q_addr + I * Cfg::kQTileBytes);
+  const uint64_t kd = smem_desc_at(kDescK, c.kv_addr + slot * Cfg::kKVTileBytes);
+  const uint32_t t_s = c.tmem_base + (I == 0 ? Cfg::kColS0 : Cfg::kColS1);
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
+    const uint32_t koff = ((kk >> 2) * Cfg::kKVPanelBytes + (kk & 3) * 32) >> 4;
+    mma_ss_elect(t_s, qd + qoff, kd + koff, kIdescQK, kk > 0);
+  }
+  mma_commit_elect(c.s_full + I);
+  if (last_user) mma_commit_elect(c.kv_empty + slot);
+  if (last_qk) mma_commit_elect(c.q_empty + I);
+}
+
+// O_i (+)= P_i . V with V in ring entry t, chunk by chunk as P arrives.
+template <class Cfg, int D, int BN, int STAGES, int I>
+__device__ __forceinline__ void wsp_issue_pv(const WspMmaCtx& c, int j, uint32_t t, bool last_user, uint32_t& pv_count,
+                                             uint32_t& resc_count, uint32_t items_done) {
+  constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kKVPanelBytes, 1024);
+  constexpr uint32_t kIdescPV = idesc_f16_f32(Cfg::BM, D, false, true);
+  constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
+  const int slot = t % STAGES;
+  mbar_wait(c.kv_full + slot, (t / STAGES) & 1, c.abort_flag, 0x902, t);
+  if (j > 0) {
+    mbar_wait(c.o_rescaled + I, resc_count & 1, c.abort_flag, 0x905 + I, j);
+    ++resc_count;
+  } else if (items_done > 0) {
+    mbar_wait(c.o_free + I, (items_done - 1) & 1, c.abort_flag, 0x907 + I, j);
+  }
+  const uint64_t vd = smem_desc_at(kDescV, c.kv_addr + slot * Cfg::kKVTileBytes);
+  const uint32_t t_p = c.tmem_base + (I == 0 ? Cfg::kColS0 : Cfg::kColS1);
+  const uint32_t t_o = c.tmem_base + (I == 0 ? Cfg::kColO0 : Cfg::kColO1);
+#pragma unroll
+  for (int q = 0; q < Cfg::kPChunks; ++q) {
+    FRAY_CRIT_WAIT(c.p_full + I * Cfg::kPChunks + q, pv_count & 1, c.abort_flag, 0x903 + I, j);
+    tc_fence_after_sync();
+#pragma unroll
+    for (int s2 = 0; s2 < kStepsPerChunk; ++s2) {
+      const int kk = q * kStepsPerChunk + s2;
+      mma_ts_elect(t_o, t_p + kk * 8, vd + ((kk * 2048) >> 4), kIdescPV, (j > 0 || kk > 0));
+    }
+  }
+  ++pv_count;
+  mma_commit_elect(c.o_full + I);
+  if (last_user) mma_commit_elect(c.kv_empty + slot);
+}
+
+// One tile's share of KV step j of item w (j = -1: the item's lead-in, where only a first Q.K^T may
+// be due).  nx is the next item of this CTA (valid when has_next).
+template <class Cfg, int D, int BN, int STAGES, int I>
+__device__ __forceinline__ void wsp_tile_step(const WspMmaCtx& c, const WspItem& w, const WspItem& nx, bool has_next,
+                                              int j, uint32_t t_base, uint32_t t_next, uint32_t& q_count,
+                                              uint32_t& pv_count, uint32_t& resc_count, uint32_t& items_done,
+                                              bool& started) {
+  const int n_i = I ? w.n1 : w.n0;
+  if (n_i == 0) return;
+  if (j >= 0 && j < n_i)
+    wsp_issue_pv<Cfg, D, BN, STAGES, I>(c, j, t_base + 2 * j + 1, (I == 1) || !(j < w.n1), pv_count, resc_count,
+                                        items_done);
+  if (j + 1 < n_i) {
+    if (j >= 0) {
+      wsp_issue_qk<Cfg, D, BN, STAGES, I>(c, t_base + 2 * (j + 1), false, (I == 1) || !(j + 1 < w.n1), j + 2 == n_i,
+                                          q_count);
+    } else {
+      if (!started) wsp_issue_qk<Cfg, D, BN, STAGES, I>(c, t_base, true, (I == 1) || !(0 < w.n1), n_i == 1, q_count);
+      started = false;
+    }
+  } else if (j + 1 == n_i) {
+    // Tile I has finished this item.  Start it on the next item right away when the ring can hold
+    // that item's K_0 beside everything the other tile still needs.
+    ++items_done;
+    const int nn_i = I ? nx.n1 : nx.n0;
+    if (has_next && nn_i > 0 && 2 * (w.n_max - n_i) + 2 <= STAGES) {
+      wsp_issue_qk<Cfg, D, BN, STAGES, I>(c, t_next, true, (I == 1) || !(0 < nx.n1), nn_i == 1, q_count);
+      started = true;
+    }
+  }
+}
+
 template <int D, int BN, int STAGES, int POLY>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -353,120 +464,26 @@ attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // the tensor pipe.  Per tile the order is K/V ring order - entry K_j: S_i(j) = Q_i.K_j^T, entry
       // V_j: O_i += P_i(j).V_j - and it carries over from one item to the next, so a tile's first
       // Q.K^T of the next item follows its last P.V directly.
-      constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);
-      constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kKVPanelBytes, 1024);
-      constexpr uint32_t kIdescQK = idesc_f16_f32(Cfg::BM, BN, false, false);
-      constexpr uint32_t kIdescPV = idesc_f16_f32(Cfg::BM, D, false, true);
-      constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
-      const uint32_t q_addr = smem_u32(q_smem);
-      const uint32_t kv_addr = smem_u32(kv_smem);
-
-      // Per-tile progress.  Every field is only touched through a compile-time tile index, so the
-      // two instances stay in registers.
-      struct TileState {
-        uint32_t q_count = 0;     // q_full phases consumed
-        uint32_t pv_count = 0;    // P.V steps issued (phase of the p_full chunks)
-        uint32_t resc_count = 0;  // o_rescaled phases consumed
-        uint32_t items_done = 0;  // items finished (phase of o_free)
-        uint32_t qk_trace = 0;    // Q.K^T batches issued (timeline index only)
-      };
-      TileState st0, st1;
-
-      // S_i = Q_i . K^T with K in ring entry t.  new_q: first use of a freshly loaded Q tile;
-      // last_user releases the ring entry, last_qk the Q buffer.
-      auto issue_qk = [&](auto tile, TileState& st, uint32_t t, bool new_q, bool last_user, bool last_qk)
-          __attribute__((always_inline)) {
-        constexpr int i = decltype(tile)::value;
-        const int slot = t % STAGES;
-        mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x901, t);
-        if (new_q) {
-          mbar_wait(q_full + i, st.q_count & 1, abort_flag, 0x911 + i, t);
-          ++st.q_count;
-        }
-        tc_fence_after_sync();
-        const uint64_t qd = smem_desc_at(kDescK, q_addr + i * Cfg::kQTileBytes);
-        const uint64_t kd = smem_desc_at(kDescK, kv_addr + slot * Cfg::kKVTileBytes);
-        constexpr uint32_t t_s_off = (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
-          const uint32_t koff = ((kk >> 2) * Cfg::kKVPanelBytes + (kk & 3) * 32) >> 4;
-          mma_ss_elect(tmem_base + t_s_off, qd + qoff, kd + koff, kIdescQK, kk > 0);
-        }
-        mma_commit_elect(s_full + i);
-        if (last_user) mma_commit_elect(kv_empty + slot);
-        if (last_qk) mma_commit_elect(q_empty + i);
-        FRAY_TRACE(8, i, st.qk_trace);
-        ++st.qk_trace;
-      };
-      // O_i (+)= P_i . V with V in ring entry t, chunk by chunk as P arrives.
-      auto issue_pv = [&](auto tile, TileState& st, int j, uint32_t t, bool last_user) __attribute__((always_inline)) {
-        constexpr int i = decltype(tile)::value;
-        const int slot = t % STAGES;
-        mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x902, t);
-        if (j > 0) {
-          mbar_wait(o_rescaled + i, st.resc_count & 1, abort_flag, 0x905 + i, j);
-          ++st.resc_count;
-        } else if (st.items_done > 0) {
-          mbar_wait(o_free + i, (st.items_done - 1) & 1, abort_flag, 0x907 + i, j);
-        }
-        const uint64_t vd = smem_desc_at(kDescV, kv_addr + slot * Cfg::kKVTileBytes);
-        constexpr uint32_t t_p_off = (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
-        constexpr uint32_t t_o_off = (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
-#pragma unroll
-        for (int q = 0; q < Cfg::kPChunks; ++q) {
-          FRAY_CRIT_WAIT(p_full + i * Cfg::kPChunks + q, st.pv_count & 1, abort_flag, 0x903 + i, j);
-          tc_fence_after_sync();
-          if (q == 0) FRAY_TRACE(5, i, st.pv_count);
-#pragma unroll
-          for (int s2 = 0; s2 < kStepsPerChunk; ++s2) {
-            const int kk = q * kStepsPerChunk + s2;
-            mma_ts_elect(tmem_base + t_o_off, tmem_base + t_p_off + kk * 8, vd + ((kk * 2048) >> 4), kIdescPV,
-                         (j > 0 || kk > 0));
-          }
-        }
-        FRAY_TRACE(7, i, st.pv_count);
-        ++st.pv_count;
-        mma_commit_elect(o_full + i);
-        if (last_user) mma_commit_elect(kv_empty + slot);
-      };
-
-      uint32_t t_base = 0;  // ring index of the current item's K_0
-      bool started0 = false, started1 = false;  // the item's first Q.K^T was issued from the previous item's tail
+      const WspMmaCtx ctx{kv_full, kv_empty, q_full, q_empty, s_full, o_full, o_rescaled, o_free, p_full,
+                          abort_flag, smem_u32(q_smem), smem_u32(kv_smem), tmem_base};
+      // per-tile progress, plain scalars
+      uint32_t q_count0 = 0, q_count1 = 0;        // q_full phases consumed
+      uint32_t pv_count0 = 0, pv_count1 = 0;      // P.V steps issued (phase of the p_full chunks)
+      uint32_t resc_count0 = 0, resc_count1 = 0;  // o_rescaled phases consumed
+      uint32_t items_done0 = 0, items_done1 = 0;  // items finished (phase of o_free)
+      bool started0 = false, started1 = false;    // first Q.K^T already issued from the previous item's tail
+      uint32_t t_base = 0;                        // ring index of the current item's K_0
       for (int item = first_item; item < n_items; item += item_step) {
         const WspItem w = wsp_decode_item<Cfg::BM, BN>(item, n_pairs, num_heads, seq_len, causal);
         const bool has_next = item + item_step < n_items;
         WspItem nx = w;
         if (has_next) nx = wsp_decode_item<Cfg::BM, BN>(item + item_step, n_pairs, num_heads, seq_len, causal);
         const uint32_t t_next = t_base + 2 * w.n_max;  // ring index of the next item's K_0
-
-        // One tile's share of KV step j (j = -1: the item's lead-in, where only a first Q.K^T may be due).
-        auto tile_step = [&](auto tile, TileState& st, bool& started, int j) __attribute__((always_inline)) {
-          constexpr int i = decltype(tile)::value;
-          const int n_i = i ? w.n1 : w.n0;
-          if (n_i == 0) return;
-          if (j >= 0 && j < n_i) issue_pv(tile, st, j, t_base + 2 * j + 1, (i == 1) || !(j < w.n1));
-          if (j + 1 < n_i) {
-            if (j >= 0) {
-              issue_qk(tile, st, t_base + 2 * (j + 1), false, (i == 1) || !(j + 1 < w.n1), j + 2 == n_i);
-            } else {
-              if (!started) issue_qk(tile, st, t_base, true, (i == 1) || !(0 < w.n1), n_i == 1);
-              started = false;
-            }
-          } else if (j + 1 == n_i) {
-            // Tile i has finished this item.  Start it on the next item right away when the ring can
-            // hold that item's K_0 beside everything the other tile still needs.
-            ++st.items_done;
-            const int nn_i = i ? nx.n1 : nx.n0;
-            if (has_next && nn_i > 0 && 2 * (w.n_max - n_i) + 2 <= STAGES) {
-              issue_qk(tile, st, t_next, true, (i == 1) || !(0 < nx.n1), nn_i == 1);
-              started = true;
-            }
-          }
-        };
         for (int j = -1; j < w.n_max; ++j) {
-          tile_step(TileTag<0>{}, st0, started0, j);
-          tile_step(TileTag<1>{}, st1, started1, j);
+          wsp_tile_step<Cfg, D, BN, STAGES, 0>(ctx, w, nx, has_next, j, t_base, t_next, q_count0, pv_count0, resc_count0,
+                                               items_done0, started0);
+          wsp_tile_step<Cfg, D, BN, STAGES, 1>(ctx, w, nx, has_next, j, t_base, t_next, q_count1, pv_count1, resc_count1,
+                                               items_done1, started1);
         }
         t_base = t_next;
       }
