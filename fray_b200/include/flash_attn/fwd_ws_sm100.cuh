@@ -186,10 +186,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
   if (tid == 0) FRAY_TRACE(6, 0, 1);  // set-up done
 
-  if (warp < 8) {
+  const int role = warp;  // (rotating the role assignment over the warp index was measured to make no difference)
+  if (role < 8) {
     // =============================================================== softmax groups
     set_max_regs_inc<Cfg::kRegsSoftmax>();
-    const int i = warp >> 2;              // query tile of this group
+    const int i = role >> 2;              // query tile of this group
     const int r = tid & 127;              // row inside the tile
     const int n_i = i ? n_t1 : n_t0;
     const int n_both = n_t0 < n_t1 ? n_t0 : n_t1;  // KV steps that both tiles run
@@ -222,7 +223,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(corr_ready + i);
     }
-  } else if (warp < 12) {
+  } else if (role < 12) {
     // =============================================================== correction group + epilogue
     set_max_regs_dec<Cfg::kRegsCorrection>();
     const int r = tid & 127;
@@ -303,7 +304,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else {
     set_max_regs_dec<Cfg::kRegsOther>();
-    if (warp == 13 && lane == 0) {
+    if (role == 13 && lane == 0) {
       // ============================================================= TMA producer
       auto load_q = [&](int i) __attribute__((always_inline)) {
         if ((i ? n_t1 : n_t0) > 0) {
@@ -327,7 +328,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                       (t >> 1) * BN, h, b);
         if (t == 0) load_q(1);
       }
-    } else if (warp == 12) {
+    } else if (role == 12) {
       // ============================================================= MMA issue (whole warp, one elected lane issues)
       // One warp serves both tiles in a fixed alternation.  That ordering is what keeps the two
       // tiles in anti-phase (one in its softmax while the other owns the tensor pipe); two
@@ -345,15 +346,17 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const int slot = t % STAGES;
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x501, t);
         tc_fence_after_sync();
-        const uint64_t qd = smem_desc_at(kDescK, q_addr + i * Cfg::kQTileBytes);
-        const uint64_t kd = smem_desc_at(kDescK, kv_addr + slot * Cfg::kKVTileBytes);
+        constexpr uint32_t kDescHi = static_cast<uint32_t>(kDescK >> 32);
+        constexpr uint32_t kDescLo = static_cast<uint32_t>(kDescK);
+        // descriptor start addresses are in 16-byte units and never carry out of the 14-bit field
+        const uint32_t q_lo = kDescLo | (((q_addr + i * Cfg::kQTileBytes) & 0x3FFFF) >> 4);
+        const uint32_t k_lo = kDescLo | (((kv_addr + slot * Cfg::kKVTileBytes) & 0x3FFFF) >> 4);
         const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          // descriptor start addresses are in 16-byte units
           const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
           const uint32_t koff = ((kk >> 2) * Cfg::kKVPanelBytes + (kk & 3) * 32) >> 4;
-          mma_ss_elect(t_s, qd + qoff, kd + koff, kIdescQK, kk > 0);
+          mma_ss_elect_lohi(t_s, q_lo + qoff, kDescHi, k_lo + koff, kDescHi, kIdescQK, kk > 0);
         }
         mma_commit_elect(s_full + i);
         if ((i == 1) || !(j < n1)) mma_commit_elect(kv_empty + slot);
@@ -364,7 +367,8 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const int slot = t % STAGES;
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x502, t);
         if (j > 0) mbar_wait(o_rescaled + i, (j - 1) & 1, abort_flag, 0x505 + i, j);
-        const uint64_t vd = smem_desc_at(kDescV, kv_addr + slot * Cfg::kKVTileBytes);
+        constexpr uint32_t kDescVHi = static_cast<uint32_t>(kDescV >> 32);
+        const uint32_t v_lo = static_cast<uint32_t>(kDescV) | (((kv_addr + slot * Cfg::kKVTileBytes) & 0x3FFFF) >> 4);
         const uint32_t t_p = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
         const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
         constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
@@ -376,7 +380,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
           for (int s2 = 0; s2 < kStepsPerChunk; ++s2) {
             const int kk = q * kStepsPerChunk + s2;
-            mma_ts_elect(t_o, t_p + kk * 8, vd + ((kk * 2048) >> 4), kIdescPV, (j > 0 || kk > 0));
+            mma_ts_elect_lohi(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
           }
         }
         mma_commit_elect(o_full + i);

@@ -91,6 +91,37 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Address forms: the barrier is named by its 32-bit shared-memory address.  A role that touches
+// many barriers keeps one base address and constant offsets instead of a 64-bit pointer each.
+__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar_addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar_addr), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait_a(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag,
+                                            uint32_t site, uint32_t extra = 0) {
+  if (mbar_try_wait_a(bar_addr, parity)) return;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (!mbar_try_wait_a(bar_addr, parity)) {
+    if ((++polls & 31u) == 0u) {
+      if (*abort_flag) return;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        report_timeout(abort_flag, site, extra);
+        return;
+      }
+    }
+  }
+}
+
 // Same contract as mbar_wait, but polls with the non-blocking test_wait instead of the suspending
 // try_wait.  A suspended waiter was measured to resume a few hundred cycles after the barrier
 // flips; on the hand-overs that sit on the critical path (scores ready, probabilities ready) a
@@ -256,6 +287,41 @@ __device__ __forceinline__ void mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, u
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Split-descriptor forms: the shared-memory descriptors are passed as (low, high) 32-bit halves
+// and joined inside the instruction block.  Only the low half (the start address) changes from
+// one K step to the next, so an unrolled issue sequence needs one 32-bit value per operand and
+// step instead of a 64-bit pair, which keeps the issuing warp inside a small register budget.
+__device__ __forceinline__ void mma_ss_elect_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                  uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, e;\n"
+      ".reg .b64 da, db;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_elect_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p, e;\n"
+      ".reg .b64 db;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void mma_commit_elect(uint64_t* bar) {
   asm volatile(
       "{\n"
@@ -263,6 +329,16 @@ __device__ __forceinline__ void mma_commit_elect(uint64_t* bar) {
       "elect.sync _|e, 0xffffffff;\n"
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
       "}\n" ::"r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_commit_elect_a(uint32_t bar_addr) {
+  asm volatile(
+      "{\n"
+      ".reg .pred e;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+      "}\n" ::"r"(bar_addr)
       : "memory");
 }
 
