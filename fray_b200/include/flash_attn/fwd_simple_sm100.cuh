@@ -237,11 +237,11 @@ inline int launch_attn_fwd_simple(const __half* q, const __half* k, const __half
                                   const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
   using Cfg = SimpleCfg<D, BN>;
   CUtensorMap tm_q, tm_k, tm_v;
-  int rc = make_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
+  int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
-  rc = make_attn_tensor_map(&tm_k, k, shp, st[1], BN);
+  rc = cached_attn_tensor_map(&tm_k, k, shp, st[1], BN);
   if (rc != kAttnOk) return rc;
-  rc = make_attn_tensor_map(&tm_v, v, shp, st[2], BN);
+  rc = cached_attn_tensor_map(&tm_v, v, shp, st[2], BN);
   if (rc != kAttnOk) return rc;
 
   auto kernel = attn_fwd_simple_kernel<D, BN>;

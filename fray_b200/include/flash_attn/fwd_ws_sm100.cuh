@@ -426,13 +426,13 @@ inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v,
                               const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
   using Cfg = WsCfg<D, BN, STAGES>;
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
-  int rc = make_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
+  int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
-  rc = make_attn_tensor_map(&tm_k, k, shp, st[1], BN);
+  rc = cached_attn_tensor_map(&tm_k, k, shp, st[1], BN);
   if (rc != kAttnOk) return rc;
-  rc = make_attn_tensor_map(&tm_v, v, shp, st[2], BN);
+  rc = cached_attn_tensor_map(&tm_v, v, shp, st[2], BN);
   if (rc != kAttnOk) return rc;
-  rc = make_attn_tensor_map(&tm_o, o, shp, st[3], Cfg::BM);
+  rc = cached_attn_tensor_map(&tm_o, o, shp, st[3], Cfg::BM);
   if (rc != kAttnOk) return rc;
 
   static_assert(POLY >= 0 && POLY <= 4, "POLY counts polynomial pairs out of every 4");

@@ -89,6 +89,42 @@ inline int make_attn_tensor_map(CUtensorMap* map, const void* base, const AttnSh
   return r == CUDA_SUCCESS ? kAttnOk : kAttnTensorMapFailed;
 }
 
+// Same as make_attn_tensor_map, but remembers the last few encodings per host thread: a caller that
+// launches on the same buffers again (the common case: a fixed set of activations per layer, or a
+// benchmark loop) skips the driver call.  A tensor map depends only on the key compared below.
+inline int cached_attn_tensor_map(CUtensorMap* map, const void* base, const AttnShape& shp, const AttnStrides& st,
+                                  int box_rows) {
+  struct Entry {
+    const void* base = nullptr;
+    AttnShape shp{0, 0, 0, 0};
+    AttnStrides st{0, 0, 0};
+    int box_rows = 0;
+    CUtensorMap map;
+  };
+  constexpr int kEntries = 16;
+  thread_local Entry cache[kEntries];
+  thread_local int next = 0;
+  for (int e = 0; e < kEntries; ++e) {
+    const Entry& c = cache[e];
+    if (c.base == base && c.box_rows == box_rows && c.shp.B == shp.B && c.shp.H == shp.H && c.shp.S == shp.S &&
+        c.shp.D == shp.D && c.st.b == st.b && c.st.h == st.h && c.st.s == st.s) {
+      *map = c.map;
+      return kAttnOk;
+    }
+  }
+  const int rc = make_attn_tensor_map(map, base, shp, st, box_rows);
+  if (rc == kAttnOk) {
+    Entry& c = cache[next];
+    next = (next + 1) % kEntries;
+    c.base = base;
+    c.shp = shp;
+    c.st = st;
+    c.box_rows = box_rows;
+    c.map = *map;
+  }
+  return rc;
+}
+
 // Synchronising read of the sticky device status words; clears them when asked.
 inline int read_attn_status(int* out4, bool clear) {
   int host[4] = {0, 0, 0, 0};

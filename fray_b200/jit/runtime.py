@@ -11,7 +11,7 @@ from typing import Dict, Optional
 
 import torch
 
-from .template import map_ctype
+from .template import ctype_map, map_ctype
 
 _REQUIRED_FILES = ("kernel.cu", "kernel.args", "kernel.so")
 
@@ -35,6 +35,8 @@ class Runtime:
             self.args = eval(f.read(), {"__builtins__": {}}, {"torch": torch, "int": int, "float": float, "bool": bool})
         if self.args and not isinstance(self.args[0], tuple):
             self.args = (self.args,)
+        # Declared argument types let callers on a fast path pass plain Python numbers.
+        self.lib.launch.argtypes = [ctype_map[kind] for _, kind in self.args] + [ctypes.POINTER(ctypes.c_int)]
 
     def __call__(self, *args) -> int:
         if self.lib is None:
@@ -50,6 +52,16 @@ class Runtime:
         return_code = ctypes.c_int(0)
         self.lib.launch(*cargs, ctypes.byref(return_code))
         return return_code.value
+
+    def raw_launch(self):
+        """The bound ``launch`` symbol itself, for callers that have validated and marshalled once already.
+
+        Arguments are plain numbers (pointers and streams as integers) followed by
+        ``ctypes.byref(ctypes.c_int)`` for the return code; no per-argument checks are made.
+        """
+        if self.lib is None:
+            self._load()
+        return self.lib.launch
 
     def symbol(self, name: str):
         """An extra exported symbol of the library, or None when it has none by that name."""

@@ -8,6 +8,7 @@ extensions.  Unlike the reference, strided views whose last dimension is contigu
 consumed and produced through their strides (no hidden copies, and a non-contiguous
 ``Output`` really receives the result).
 """
+import ctypes
 import math
 import os
 from typing import Any, Dict, Optional, Tuple
@@ -122,6 +123,10 @@ def prebuild(head_dims=SUPPORTED_HEAD_DIMS, prune: bool = False):
 
 
 _last_runtime = None
+# Warm-call fast path: (shapes, strides, dtypes, devices, causal, scale) -> (runtime, launch symbol, int args).
+# Everything the slow path validates is a function of that key, so a hit only has to marshal the
+# four pointers and the stream.
+_fast_path: Dict[Any, Any] = {}
 
 
 def flash_attn_status(clear: bool = True) -> Tuple[int, int, int, int]:
@@ -132,7 +137,6 @@ def flash_attn_status(clear: bool = True) -> Tuple[int, int, int, int]:
     number.  The status is sticky: until cleared, later launches of that library return
     immediately without computing.
     """
-    import ctypes
     if _last_runtime is None:
         return (0, 0, 0, 0)
     fn = _last_runtime.symbol("fray_attn_status")
@@ -147,6 +151,19 @@ def flash_attn_status(clear: bool = True) -> Tuple[int, int, int, int]:
 def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: torch.Tensor, *,
                     causal: bool = False, scale: Optional[float] = None) -> None:
     global _last_runtime
+    fast_key = (Q.shape, Q.stride(), K.shape, K.stride(), V.shape, V.stride(), Output.shape, Output.stride(),
+                Q.dtype, K.dtype, V.dtype, Output.dtype, Q.device, K.device, V.device, Output.device,
+                bool(causal), scale, os.getenv("FRAY_ATTN_FORCE"))
+    hit = _fast_path.get(fast_key)
+    if hit is not None:
+        runtime, launch, ints, sm_scale = hit
+        rc = ctypes.c_int(0)
+        launch(Q.data_ptr(), K.data_ptr(), V.data_ptr(), Output.data_ptr(), *ints, bool(causal), sm_scale,
+               torch.cuda.current_stream().cuda_stream, ctypes.byref(rc))
+        if rc.value == 0:
+            _last_runtime = runtime
+            return
+        # e.g. a misaligned data pointer this time: let the checked path deal with it
     assert Q.dim() == 4, "expected [B, H, S, D] tensors"
     batch_size, num_heads, seq_len, d = Q.shape
     assert Q.shape == K.shape == V.shape == Output.shape
@@ -191,5 +208,8 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
         rc = runtime(*pack(q, k, v, out))
     if rc != 0:
         raise RuntimeError(f"flash_attn_cute launch failed with code {rc} ({_RC_TEXT.get(rc, 'unknown')})")
+    if q is Q and k is K and v is V and out is Output:
+        # no copies were needed: remember how to launch this layout directly
+        _fast_path[fast_key] = (runtime, runtime.raw_launch(), args[4:4 + 3 + 12], sm_scale)
     if out is not Output:
         Output.copy_(out)
