@@ -16,6 +16,7 @@ enum AttnKernelKind : int {
   kAttnSimple = 0,  // one 128-row tile per CTA, single role, no overlap
   kAttnWarpSpecialized = 1,  // two 128-row tiles per CTA, producer / MMA / softmax / correction roles
   kAttnPersistent = 2,       // the same roles in one CTA per SM that loops over work items
+  kAttnSplitRow = 3,         // the warp-specialised kernel with two softmax threads per query row (24 warps)
 };
 
 // KIND, D, BLOCK_N, STAGES, POLY are compile-time tuning keys (POLY: how many of every four
@@ -35,6 +36,12 @@ inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, 
     rc = sm100::launch_attn_fwd_simple<D, BLOCK_N>(q, k, v, o, shp, st, causal, scale, stream);
   } else if constexpr (KIND == kAttnWarpSpecialized) {
     rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);
+  } else if constexpr (KIND == kAttnSplitRow) {
+    // POLY picks how a row is divided: 0 = 64 + 64 keys, both on the special-function unit;
+    // 1 = 80 + 48 and 2 = 96 + 32 keys with the smaller part on the polynomial.
+    static_assert(POLY >= 0 && POLY <= 2, "split-row kernel: POLY is 0, 1 or 2");
+    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, 0, 2, (POLY == 0 ? 64 : POLY == 1 ? 80 : 96)>(
+        q, k, v, o, shp, st, causal, scale, stream);
   } else {
     static_assert(KIND == kAttnPersistent, "unknown kernel kind");
     rc = sm100::launch_attn_fwd_wsp<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);

@@ -26,6 +26,11 @@
 // 1 (at most 256, exact in fp16 range) and O needs no correction.  O and l always share the
 // same m_ref, so the final O/l is the exact softmax up to rounding.
 //
+// Split-row variant (SPLIT = 2, 24 warps): each query tile gets two softmax warpgroups; the first
+// works on keys [0,KA) of every tile, the second on keys [KA,128) of the same rows, with its
+// exponentials on the FMA pipe when KA > 64 (see softmax_part_tile).  Warps 0-7 then serve tile 0,
+// warps 8-15 tile 1, and the correction / MMA / producer warps follow.
+//
 // Every barrier wait is bounded (see sm100_ptx.cuh): a protocol error ends as a status
 // word and a wrong answer, never as a hung GPU.
 
@@ -33,17 +38,49 @@
 #include "sm100_ptx.cuh"
 #include "softmax_tile_sm100.cuh"
 
+// Per-thread register budgets of the three kinds of warps (softmax, correction, MMA/producer), each a
+// multiple of 8; 256*S + 128*C + 128*O must not exceed the 64K registers of an SM.
+#ifndef FRAY_WS_REGS_S
+#define FRAY_WS_REGS_S 184
+#endif
+#ifndef FRAY_WS_REGS_C
+#define FRAY_WS_REGS_C 80
+#endif
+#ifndef FRAY_WS_REGS_O
+#define FRAY_WS_REGS_O 64
+#endif
+// The same for the split-row variant.  setmaxnreg only moves registers inside the CTA's own
+// allocation (threads x registers at launch = 768 x 80 here, not the whole register file), and an
+// increase that the decreases of the other warps cannot cover blocks for ever:
+// 256*(A + B) + 128*C + 128*O <= 768*80, where the two softmax groups of a tile get A and B
+// registers according to the number of keys each holds (see WsCfg).
+#ifndef FRAY_WS2_REGS_C
+#define FRAY_WS2_REGS_C 72
+#endif
+#ifndef FRAY_WS2_REGS_O
+#define FRAY_WS2_REGS_O 56
+#endif
+
 namespace fray {
 namespace sm100 {
 
-template <int D, int BN, int STAGES>
+template <int D, int BN, int STAGES, int SPLIT = 1, int KA = 64>
 struct WsCfg {
+  static_assert(KA == 64 || KA == 80 || KA == 96, "keys of a tile that the first softmax group of a split row takes");
+  static_assert(SPLIT == 2 || KA == 64, "KA only applies to split rows");
+  static_assert(SPLIT == 1 || SPLIT == 2, "one or two softmax threads per query row");
   static_assert(D == 64 || D == 128, "head dim must be 64 or 128");
   static_assert(BN == 128, "the warp-specialised kernel uses 128-key tiles");
   static_assert(STAGES >= 2 && STAGES <= 8, "2..8 K/V buffers");
   static constexpr int BM = 128;               // rows per query tile
-  static constexpr int kPChunks = 4;           // P is handed to the MMA warp in this many column chunks
-  static constexpr int kThreads = 512;
+  // P is handed to the MMA warp in this many column chunks; chunk q covers chunk_steps(q) MMAs of 16 keys.
+  static constexpr int kPChunks = (SPLIT == 2 && KA == 80) ? 5 : 4;
+  static constexpr int kChunksA = SPLIT == 1 ? 4 : (KA == 64 ? 2 : 3);  // chunks written by the first group
+  __host__ __device__ static constexpr int chunk_steps(int q) {
+    return (SPLIT == 2 && KA == 80 && (q == 2 || q == 3)) ? 1 : 2;
+  }
+  static constexpr int kSoftmaxWarps = 8 * SPLIT;
+  static constexpr int kThreads = 32 * (kSoftmaxWarps + 8);
   static constexpr int kPanels = D / 64;       // 64-element (128-byte) column panels
   static constexpr int kQPanelBytes = BM * 128;
   static constexpr int kQTileBytes = kPanels * kQPanelBytes;
@@ -54,17 +91,33 @@ struct WsCfg {
   static constexpr int kOffBars = kOffKV + STAGES * kKVTileBytes;
   static constexpr int kNumBars = 2 + 2 * STAGES + 2 * 5 + 2 * kPChunks;
   static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][128], l[2][128]
+  static constexpr int kOffXchg = kOffStats + 4 * 128 * 4;  // half-row maxima [2 parities][2 tiles][2 halves][128]
+  static constexpr int kXchgBytes = SPLIT == 2 ? 2 * 2 * 2 * 128 * 4 : 0;
 #ifdef FRAY_ATTN_TRACE
-  static constexpr int kOffTrace = kOffStats + 4 * 128 * 4;
+  static constexpr int kOffTrace = kOffXchg + kXchgBytes;
   static constexpr int kSmemBytes = kOffTrace + 4 * 800 + 1024;
 #else
-  static constexpr int kSmemBytes = kOffStats + 4 * 128 * 4 + 1024;                    // + alignment slack
+  static constexpr int kSmemBytes = kOffXchg + kXchgBytes + 1024;                      // + alignment slack
 #endif
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of one CTA");
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
   // register budgets after setmaxnreg (sum over 16 warps = 64K registers)
-  static constexpr int kRegsSoftmax = 184, kRegsCorrection = 80, kRegsOther = 64;
+#ifdef FRAY_WS2_REGS_A
+  static constexpr int kRegsSoftmax = SPLIT == 2 ? FRAY_WS2_REGS_A : FRAY_WS_REGS_S;
+#else
+  static constexpr int kRegsSoftmax = SPLIT == 2 ? (KA == 64 ? 88 : KA == 80 ? 96 : 112) : FRAY_WS_REGS_S;
+#endif
+  static constexpr int kRegsSoftmaxB = SPLIT == 2 ? 176 - kRegsSoftmax : kRegsSoftmax;  // second group of a split row
+  static constexpr int kRegsCorrection = SPLIT == 2 ? FRAY_WS2_REGS_C : FRAY_WS_REGS_C;
+  static constexpr int kRegsOther = SPLIT == 2 ? FRAY_WS2_REGS_O : FRAY_WS_REGS_O;
+  // Registers per thread the CTA is launched with: what __launch_bounds__(kThreads, 1) lets ptxas use.
+  static constexpr int kRegsAtLaunch = (65536 / kThreads) / 8 * 8;
+  static_assert(kSoftmaxWarps * 16 * (kRegsSoftmax + kRegsSoftmaxB) + 128 * kRegsCorrection + 128 * kRegsOther <=
+                    kThreads * kRegsAtLaunch,
+                "register budgets exceed the CTA's allocation: setmaxnreg.inc would never return");
+  static_assert(kRegsCorrection <= kRegsAtLaunch && kRegsOther <= kRegsAtLaunch && kRegsSoftmax >= kRegsAtLaunch,
+                "setmaxnreg.dec must not raise and .inc must not lower the count");
 };
 
 
@@ -74,6 +127,9 @@ struct WsCfg {
 // Compiled out by default.
 #ifndef FRAY_TRACE_ROW
 #define FRAY_TRACE_ROW 0  // which row's thread stamps the softmax events
+#endif
+#ifndef FRAY_TRACE_PART
+#define FRAY_TRACE_PART 0  // split rows: which of the row's two threads stamps them
 #endif
 #ifdef FRAY_ATTN_TRACE
 static constexpr int kTraceEvents = 10, kTraceIters = 40;
@@ -94,12 +150,12 @@ inline int read_attn_trace(unsigned int* out, int max_words) {
 #endif
 
 
-template <int D, int BN, int STAGES, int POLY>
-__global__ void __launch_bounds__(512, 1)
+template <int D, int BN, int STAGES, int POLY, int SPLIT, int KA>
+__global__ void __launch_bounds__(256 + 256 * SPLIT, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                    int num_heads, int seq_len, int causal, float scale_log2) {
-  using Cfg = WsCfg<D, BN, STAGES>;
+  using Cfg = WsCfg<D, BN, STAGES, SPLIT, KA>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
@@ -119,6 +175,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
   float* alpha_buf = reinterpret_cast<float*>(smem + Cfg::kOffStats);  // [2][128]
   float* l_buf = alpha_buf + 256;                                      // [2][128]
+  float* xchg = reinterpret_cast<float*>(smem + Cfg::kOffXchg);        // [2][2][2][128], split-row variant only
 
 #ifdef FRAY_ATTN_TRACE
   unsigned int* trace_sm = reinterpret_cast<unsigned int*>(smem + Cfg::kOffTrace);
@@ -186,42 +243,93 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
   if (tid == 0) FRAY_TRACE(6, 0, 1);  // set-up done
 
-  const int role = warp;  // (rotating the role assignment over the warp index was measured to make no difference)
+  // (rotating the role assignment over the warp index was measured to make no difference)
+  const int role = warp < Cfg::kSoftmaxWarps ? 0 : warp - Cfg::kSoftmaxWarps + 8;
   if (role < 8) {
     // =============================================================== softmax groups
-    set_max_regs_inc<Cfg::kRegsSoftmax>();
-    const int i = role >> 2;              // query tile of this group
+    const int i = warp / (4 * SPLIT);     // query tile of this group
     const int r = tid & 127;              // row inside the tile
     const int n_i = i ? n_t1 : n_t0;
-    const int n_both = n_t0 < n_t1 ? n_t0 : n_t1;  // KV steps that both tiles run
     const int row = m0 + i * Cfg::BM + r;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1) + lane_base;
+    uint64_t* p_bar = p_full + i * Cfg::kPChunks;
     float m_ref = -INFINITY;  // exponent offset currently baked into P, l and O
     float l_run = 0.f;
 
-    static_assert(Cfg::kPChunks == kSoftmaxPChunks, "softmax_tile hands P over in kSoftmaxPChunks chunks");
-    uint64_t* p_bar = p_full + i * Cfg::kPChunks;
+    if constexpr (SPLIT == 1) {
+      set_max_regs_inc<Cfg::kRegsSoftmax>();
+      static_assert(SPLIT == 2 || Cfg::kPChunks == kSoftmaxPChunks, "softmax_tile hands P over in kSoftmaxPChunks chunks");
+      const int n_both = n_t0 < n_t1 ? n_t0 : n_t1;  // KV steps that both tiles run
+      for (int j = 0; j < n_i; ++j) {
+        FRAY_CRIT_WAIT(s_full + i, j & 1, abort_flag, 0x201 + i, j);
+        tc_fence_after_sync();
+        if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
 
-    for (int j = 0; j < n_i; ++j) {
-      FRAY_CRIT_WAIT(s_full + i, j & 1, abort_flag, 0x201 + i, j);
-      tc_fence_after_sync();
-      if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
-
-      const int kv0 = j * BN;
-      const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
-      // Steps both tiles run take turns on the special-function unit; tile 0 goes first (its first
-      // wait uses the parity of the phase "before" the barrier's first one, which reads as complete).
-      const bool take_turns = kSfuTurns && j < n_both;
-      softmax_tile<BN, POLY>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, need_mask, kv0, row, seq_len,
-                             causal, scale_log2, lane, m_ref, l_run, take_turns ? sfu_turn + i : nullptr,
-                             take_turns ? sfu_turn + (1 - i) : nullptr, (j + 1 - i) & 1, abort_flag);
-      if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
-    }
-    if (n_i > 0) {
-      l_buf[i * 128 + r] = l_run;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(corr_ready + i);
+        const int kv0 = j * BN;
+        const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+        // Steps both tiles run take turns on the special-function unit; tile 0 goes first (its first
+        // wait uses the parity of the phase "before" the barrier's first one, which reads as complete).
+        const bool take_turns = kSfuTurns && j < n_both;
+        softmax_tile<BN, POLY>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, need_mask, kv0, row,
+                               seq_len, causal, scale_log2, lane, m_ref, l_run, take_turns ? sfu_turn + i : nullptr,
+                               take_turns ? sfu_turn + (1 - i) : nullptr, (j + 1 - i) & 1, abort_flag);
+        if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
+      }
+      if (n_i > 0) {
+        l_buf[i * 128 + r] = l_run;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(corr_ready + i);
+      }
+    } else {
+      // Two groups per tile: the first takes keys [0,KA) of every step, the second keys [KA,128).
+      auto part_role = [&](auto part_tag) __attribute__((always_inline)) {
+        constexpr int PART = decltype(part_tag)::value;
+        for (int j = 0; j < n_i; ++j) {
+          FRAY_CRIT_WAIT(s_full + i, j & 1, abort_flag, 0x201 + i, j);
+          tc_fence_after_sync();
+          if (r == FRAY_TRACE_ROW && PART == FRAY_TRACE_PART) FRAY_TRACE(0, i, j);
+          const int kv0 = j * BN;
+          const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+          float* x = xchg + (((j & 1) * 2 + i) * 2) * 128 + r;
+          unsigned int* tr = nullptr;
+#ifdef FRAY_ATTN_TRACE
+          if (trace_on && r == FRAY_TRACE_ROW && PART == FRAY_TRACE_PART && j < kTraceIters) tr = trace_sm + i * kTraceIters + j;
+#endif
+          if constexpr (PART == 0) {
+            softmax_part_tile<BN, 0, KA, false, 0>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, x, x + 128,
+                                                   2 + i, j == 0, need_mask, kv0, row, seq_len, causal, scale_log2,
+                                                   lane, m_ref, l_run, tr);
+          } else {
+            softmax_part_tile<BN, KA, BN - KA, (KA > 64), Cfg::kChunksA>(
+                t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, x + 128, x, 2 + i, j == 0, need_mask, kv0, row,
+                seq_len, causal, scale_log2, lane, m_ref, l_run, tr);
+          }
+          if (r == FRAY_TRACE_ROW && PART == FRAY_TRACE_PART) FRAY_TRACE(4, i, j);
+        }
+        if (n_i > 0) {
+          // the row sum is the sum of the two parts' partial sums (both carry the same offset)
+          float* x = xchg + (((n_i & 1) * 2 + i) * 2) * 128 + r;
+          if constexpr (PART == 1) *x = l_run;
+          named_barrier_sync(2 + i, 256);
+          if constexpr (PART == 0) {
+            l_buf[i * 128 + r] = l_run + *x;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(corr_ready + i);
+          }
+        }
+      };
+      if (((warp >> 2) & 1) == 0) {
+        set_max_regs_inc<Cfg::kRegsSoftmax>();
+        part_role(SmInt<0>{});
+      } else {
+        if constexpr (Cfg::kRegsSoftmaxB >= Cfg::kRegsAtLaunch) {
+          set_max_regs_inc<Cfg::kRegsSoftmaxB>();
+        } else {
+          set_max_regs_dec<Cfg::kRegsSoftmaxB>();
+        }
+        part_role(SmInt<1>{});
+      }
     }
   } else if (role < 12) {
     // =============================================================== correction group + epilogue
@@ -304,7 +412,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     }
   } else {
     set_max_regs_dec<Cfg::kRegsOther>();
-    if (role == 13 && lane == 0) {
+    if (role == 13 && lane == 0) {  // second warp of the last warpgroup
       // ============================================================= TMA producer
       auto load_q = [&](int i) __attribute__((always_inline)) {
         if ((i ? n_t1 : n_t0) > 0) {
@@ -371,17 +479,15 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         const uint32_t v_lo = static_cast<uint32_t>(kDescV) | (((kv_addr + slot * Cfg::kKVTileBytes) & 0x3FFFF) >> 4);
         const uint32_t t_p = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
         const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
-        constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
+        int kk = 0;  // MMA (16 keys) inside the step; a compile-time value after unrolling
 #pragma unroll
         for (int q = 0; q < Cfg::kPChunks; ++q) {
           FRAY_CRIT_WAIT(p_full + i * Cfg::kPChunks + q, j & 1, abort_flag, 0x503 + i, j);
           tc_fence_after_sync();
           if (q == 0) FRAY_TRACE(5, i, j);
 #pragma unroll
-          for (int s2 = 0; s2 < kStepsPerChunk; ++s2) {
-            const int kk = q * kStepsPerChunk + s2;
+          for (int s2 = 0; s2 < Cfg::chunk_steps(q); ++s2, ++kk)
             mma_ts_elect_lohi(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
-          }
         }
         mma_commit_elect(o_full + i);
         if ((i == 1) || !(j < n1)) mma_commit_elect(kv_empty + slot);
@@ -421,10 +527,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 }
 
 // Host launcher for the warp-specialised kernel. Returns an AttnReturnCode.
-template <int D, int BN, int STAGES, int POLY>
+template <int D, int BN, int STAGES, int POLY, int SPLIT = 1, int KA = 64>
 inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
                               const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
-  using Cfg = WsCfg<D, BN, STAGES>;
+  using Cfg = WsCfg<D, BN, STAGES, SPLIT, KA>;
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
@@ -435,8 +541,8 @@ inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v,
   rc = cached_attn_tensor_map(&tm_o, o, shp, st[3], Cfg::BM);
   if (rc != kAttnOk) return rc;
 
-  static_assert(POLY >= 0 && POLY <= 4, "POLY counts polynomial pairs out of every 4");
-  auto kernel = attn_fwd_ws_kernel<D, BN, STAGES, POLY>;
+  static_assert((POLY >= 0 && POLY <= 4) || POLY == kExpPackedHalf, "POLY: 0..4 polynomial pairs of 4, or 16 = packed fp16");
+  auto kernel = attn_fwd_ws_kernel<D, BN, STAGES, POLY, SPLIT, KA>;
   static bool attr_done = false;  // one process drives one GPU: set once
   if (!attr_done) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {

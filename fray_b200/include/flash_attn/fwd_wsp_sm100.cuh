@@ -504,7 +504,7 @@ template <int D, int BN, int STAGES, int POLY>
 inline int launch_attn_fwd_wsp(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
                                const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
   using Cfg = WspCfg<D, BN, STAGES>;
-  static_assert(POLY >= 0 && POLY <= 4, "POLY counts polynomial pairs out of every 4");
+  static_assert((POLY >= 0 && POLY <= 4) || POLY == kExpPackedHalf, "POLY: 0..4 polynomial pairs of 4, or 16 = packed fp16");
   CUtensorMap tm_q, tm_k, tm_v;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;

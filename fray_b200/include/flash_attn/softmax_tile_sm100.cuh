@@ -13,6 +13,12 @@
 namespace fray {
 namespace sm100 {
 
+// Compile-time integer tag for generic lambdas.
+template <int V>
+struct SmInt {
+  static constexpr int value = V;
+};
+
 template <int N>
 __device__ __forceinline__ void set_max_regs_inc() {
   asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
@@ -40,10 +46,20 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 #endif
 static constexpr bool kSfuTurns = FRAY_SFU_TURNS != 0;
 
+// Timeline stamps inside the softmax step (compiled in with -DFRAY_ATTN_TRACE only): `tr` points at
+// this step's slot of event 0 in the caller's table, or is null; event e lives e*80 words further.
+#ifdef FRAY_ATTN_TRACE
+#define FRAY_SM_TRACE(tr, e) do { if ((tr) != nullptr) (tr)[(e) * 80] = static_cast<unsigned int>(clock64()); } while (0)
+#else
+#define FRAY_SM_TRACE(tr, e) do { } while (0)
+#endif
+
 // Lazy-rescale threshold in the scaled base-2 domain: offsets move only when the max grew by > 2^8.
 static constexpr float kRescaleThreshold = 8.0f;
 // P is handed to the MMA warp in this many column chunks (one mbarrier each, one arrival per warp).
 static constexpr int kSoftmaxPChunks = 4;
+// Value of the POLY tuning key that selects packed fp16 exponentials.
+static constexpr int kExpPackedHalf = 16;
 
 // t_s        tensor-memory address of this thread's lane at column 0 of the S tile (P overwrites it)
 // p_bar      kSoftmaxPChunks consecutive mbarriers, arrival count 4 (one per warp of the group)
@@ -57,7 +73,14 @@ static constexpr int kSoftmaxPChunks = 4;
 //            exponentials while the other owns the tensor pipe.
 // first_tile no running state yet: the tile max becomes the offset, nothing is published
 // need_mask  some key of the tile is past seq_len or above the causal diagonal
-// POLY       of every 4 element pairs, how many take the polynomial exp2 instead of MUFU
+// POLY       exponential mode: 0..4 = of every 4 element pairs, how many take the polynomial exp2
+//            instead of the fp32 special-function instruction; kExpPackedHalf (16) = the scaled
+//            scores are rounded to fp16 first and two exponentials are taken per instruction
+//            (ex2.approx.f16x2), the fp16 results being P itself; the row sum is then gathered in
+//            fp16 groups of 8 before it joins the fp32 total.  P is rounded to fp16 for the P.V
+//            product in every mode; the packed mode also rounds the exponent argument, which costs
+//            about 2x in calc_diff (1e-7 instead of 4e-8, against a bound of 1e-5) and halves the
+//            special-function work, the scarcest resource of this kernel.
 template <int BN, int POLY>
 __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
                                              bool first_tile, bool need_mask, int kv0, int row, int seq_len, int causal,
@@ -120,6 +143,47 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
   }
   const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
 
+  if constexpr (POLY == kExpPackedHalf) {
+    // Packed mode: one chunk of 32 keys at a time, exponentials, row sum and the store together.
+    uint32_t acc[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) acc[q] = 0u;  // +0.0 twice
+    auto chunk16 = [&](const uint32_t (&h)[64], int off, int q) {
+      uint32_t pk[kChunkCols / 2];
+#pragma unroll
+      for (int c = 0; c < kChunkCols; c += 2) {
+        const float x0 = fmaf(__uint_as_float(h[off + c]), scale_log2, neg_m);
+        const float x1 = fmaf(__uint_as_float(h[off + c + 1]), scale_log2, neg_m);
+        const uint32_t p = ex2_approx_f16x2(pack_half2(x0, x1));
+        acc[(c >> 1) & 7] = add_f16x2(acc[(c >> 1) & 7], p);  // 8 terms of at most 2^8 each per slot
+        pk[c >> 1] = p;
+      }
+      tmem_st_x16(t_s + q * (kChunkCols / 2), pk);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_bar + q);
+    };
+    uint32_t sb2[64];
+    load_half(sb2, 1);  // second half again; it sits at columns [64,128), clear of chunks 0 and 1
+    chunk16(sa, 0, 0);
+    chunk16(sa, 32, 1);
+    tmem_wait_ld();
+    if (need_mask) mask_half(sb2, 1);
+    chunk16(sb2, 0, 2);
+    chunk16(sb2, 32, 3);
+    float r0 = 0.f, r1 = 0.f;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float lo, hi;
+      unpack_half2(acc[q], lo, hi);
+      r0 += lo;
+      r1 += hi;
+    }
+    l_run += r0 + r1;
+    return;
+  }
+
   float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
   // h[...] <- exp2(S*c - m*c) for one 64-key half, in place.
   auto exp_half = [&](uint32_t (&h)[64]) {
@@ -176,6 +240,156 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
   }
   store_publish(sb2, 0, 2);
   store_publish(sb2, 32, 3);
+  l_run += (rs0 + rs1) + (rs2 + rs3);
+}
+
+
+// The same step with TWO threads per query row (threads of two warpgroups that share the row's 32
+// tensor-memory lanes).  This thread owns keys [KEY0, KEY0 + NKEYS) of the tile; the first part
+// (KEY0 == 0) takes its exponentials from the special-function unit, the second part may take them
+// from the polynomial (USE_POLY).  The unit delivers 16 exponentials per clock and SM, which for a
+// 128 x 128 tile is exactly the time the tensor pipe needs for the tile's two products, so a softmax
+// that uses nothing else can never hide behind the tensor work.  A warp that mixes both kinds of
+// exponential stalls on the unit's queue with its polynomial work still unissued behind it; giving
+// the two kinds to two warps of the same scheduler lets them overlap: one warp is bound by the
+// unit, the other by instruction issue.
+//
+// The two threads of a row must agree on the exponent offset, so each publishes the max of its
+// part in shared memory (xchg_mine / xchg_other, double-buffered by the caller over the step
+// parity) and both meet on the named barrier pair_barrier (256 threads: the two warpgroups of the
+// tile).  That barrier also orders the P stores of the second part (which land in columns below
+// 64) behind the first part's loads of the scores that sit there.  Both threads keep the same
+// m_ref; each keeps the partial row sum of its own keys (the caller adds the two at the end); the
+// first part publishes alpha.
+//
+// P is handed over in pieces of 32 keys (16 where a part begins or ends on an odd multiple of 16);
+// piece n of this part arrives on p_bar[CHUNK0 + n].
+template <int BN, int KEY0, int NKEYS, bool USE_POLY, int CHUNK0>
+__device__ __forceinline__ void softmax_part_tile(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
+                                                  float* xchg_mine, const float* xchg_other, int pair_barrier,
+                                                  bool first_tile, bool need_mask, int kv0, int row, int seq_len,
+                                                  int causal, float scale_log2, int lane, float& m_ref, float& l_run,
+                                                  unsigned int* tr = nullptr) {
+  static_assert(BN == 128, "written for 128-key tiles");
+  static_assert(KEY0 % 16 == 0 && NKEYS % 16 == 0 && NKEYS >= 32 && KEY0 + NKEYS <= BN, "parts are multiples of 16 keys");
+  uint32_t sc[NKEYS];
+  {
+    constexpr int kFull = NKEYS / 32 * 32;
+#pragma unroll
+    for (int c = 0; c < kFull; c += 32) tmem_ld_x32(t_s + KEY0 + c, reinterpret_cast<uint32_t(&)[32]>(sc[c]));
+    if constexpr (NKEYS % 32 == 16) tmem_ld_x16(t_s + KEY0 + kFull, reinterpret_cast<uint32_t(&)[16]>(sc[kFull]));
+  }
+  tmem_wait_ld();
+#ifndef FRAY_TRACE_ST
+  FRAY_SM_TRACE(tr, 1);
+#endif
+  if (need_mask) {
+#pragma unroll
+    for (int c = 0; c < NKEYS; ++c) {
+      const int kv = kv0 + KEY0 + c;
+      if (kv >= seq_len || (causal && kv > row)) sc[c] = __float_as_uint(-INFINITY);
+    }
+  }
+  float mx[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) mx[q] = __uint_as_float(sc[q]);
+#pragma unroll
+  for (int c = 8; c < NKEYS; c += 8) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) mx[q] = fmaxf(mx[q], __uint_as_float(sc[c + q]));
+  }
+  const float m_part =
+      fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+  *xchg_mine = m_part;
+#ifndef FRAY_TRACE_ST
+  FRAY_SM_TRACE(tr, 3);
+#endif
+  named_barrier_sync(pair_barrier, 256);
+  FRAY_SM_TRACE(tr, 2);
+  const float m_new = fmaxf(fmaxf(m_part, *xchg_other), m_ref);
+  if (first_tile) {
+    m_ref = m_new;
+  } else {
+    float alpha = 1.f;
+    if ((m_new - m_ref) * scale_log2 > kRescaleThreshold) {
+      alpha = ex2_approx((m_ref - m_new) * scale_log2);
+      l_run *= alpha;
+      m_ref = m_new;
+    }
+    if constexpr (KEY0 == 0) {
+      *alpha_slot = alpha;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(corr_bar);
+    }
+  }
+  const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
+
+  float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+  // One piece of KEYS keys starting at offset OFF of this part: exponentials, row sum, fp16
+  // packing, store to the P columns, hand-over.
+  auto piece = [&](auto off_tag, auto keys_tag, int n) {
+    constexpr int OFF = decltype(off_tag)::value;
+    constexpr int KEYS = decltype(keys_tag)::value;
+    uint32_t pk[KEYS / 2];
+#pragma unroll
+    for (int c = 0; c < KEYS; c += 4) {
+      const int e = OFF + c;
+      const float x0 = fmaf(__uint_as_float(sc[e]), scale_log2, neg_m);
+      const float x1 = fmaf(__uint_as_float(sc[e + 1]), scale_log2, neg_m);
+      const float x2 = fmaf(__uint_as_float(sc[e + 2]), scale_log2, neg_m);
+      const float x3 = fmaf(__uint_as_float(sc[e + 3]), scale_log2, neg_m);
+      float p0, p1, p2, p3;
+      if constexpr (USE_POLY) {
+        p0 = ex2_poly(x0);
+        p1 = ex2_poly(x1);
+        p2 = ex2_poly(x2);
+        p3 = ex2_poly(x3);
+      } else {
+        p0 = ex2_approx(x0);
+        p1 = ex2_approx(x1);
+        p2 = ex2_approx(x2);
+        p3 = ex2_approx(x3);
+      }
+      rs0 += p0;
+      rs1 += p1;
+      rs2 += p2;
+      rs3 += p3;
+      pk[c >> 1] = pack_half2(p0, p1);
+      pk[(c >> 1) + 1] = pack_half2(p2, p3);
+    }
+#ifdef FRAY_TRACE_ST
+    if (n == 0) FRAY_SM_TRACE(tr, 1);
+#endif
+    if constexpr (KEYS == 32) {
+      tmem_st_x16(t_s + (KEY0 + OFF) / 2, pk);
+    } else {
+      tmem_st_x8(t_s + (KEY0 + OFF) / 2, pk);
+    }
+    tmem_wait_st();
+#ifdef FRAY_TRACE_ST
+    if (n == 0) FRAY_SM_TRACE(tr, 3);
+#endif
+    tc_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(p_bar + CHUNK0 + n);
+    if (n == 0) FRAY_SM_TRACE(tr, 9);
+  };
+  using I0 = SmInt<0>;
+  using I16 = SmInt<16>;
+  using I32 = SmInt<32>;
+  if constexpr (KEY0 % 32 == 16) {
+    // 16-key piece first, then 32-key pieces
+    piece(I0{}, I16{}, 0);
+    if constexpr (NKEYS >= 48) piece(I16{}, I32{}, 1);
+    if constexpr (NKEYS >= 80) piece(SmInt<48>{}, I32{}, 2);
+    if constexpr (NKEYS >= 112) piece(SmInt<80>{}, I32{}, 3);
+  } else {
+    piece(I0{}, I32{}, 0);
+    if constexpr (NKEYS >= 64) piece(I32{}, I32{}, 1);
+    if constexpr (NKEYS >= 96) piece(SmInt<64>{}, I32{}, 2);
+    if constexpr (NKEYS == 128) piece(SmInt<96>{}, I32{}, 3);
+    if constexpr (NKEYS % 32 == 16) piece(SmInt<NKEYS - 16>{}, I16{}, NKEYS / 32);
+  }
   l_run += (rs0 + rs1) + (rs2 + rs3);
 }
 

@@ -64,10 +64,9 @@ _RC_TENSOR_MAP = 6
 
 
 def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
-    """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised, 2 persistent), KV tile, KV stages, exp2 mix."""
+    """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised, 2 persistent, 3 warp-specialised with split rows), KV tile, KV stages, exp2 mix."""
     space = [
-        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},
-        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},
+        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # fp32 exponentials
         {"KIND": 0, "BLOCK_N": 128, "STAGES": 1, "POLY": 0},
         {"KIND": 0, "BLOCK_N": 64, "STAGES": 1, "POLY": 0},
     ]
@@ -81,7 +80,14 @@ def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
 
 # Built and tested, but not part of the tuning space: the persistent kernel is correct and hands
 # items over without a bubble, yet its steady state measured ~20 % slower than the non-persistent one.
-EXTRA_VARIANTS = ({"KIND": 2, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},)
+# Likewise the mix of polynomial and special-function exponentials (POLY 1..4), also measured slower.
+EXTRA_VARIANTS = (
+    {"KIND": 2, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},
+    {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},
+    {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 16},  # packed fp16 exponentials: the unit needs two passes for them, no gain
+    {"KIND": 3, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # two softmax threads per row, 64 keys each
+    {"KIND": 3, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},   # ... 80 keys on the special-function unit, 48 on the polynomial
+)
 
 
 def _seq_class(seq_len: int, units: int) -> str:
