@@ -8,6 +8,7 @@
 #include "host_sm100.cuh"
 #include "fwd_ws_sm100.cuh"
 #include "fwd_wsp_sm100.cuh"
+#include "fwd_wsh_sm100.cuh"
 
 namespace fray {
 
@@ -17,6 +18,8 @@ enum AttnKernelKind : int {
   kAttnWarpSpecialized = 1,  // two 128-row tiles per CTA, producer / MMA / softmax / correction roles
   kAttnPersistent = 2,       // the same roles in one CTA per SM that loops over work items
   kAttnSplitRow = 3,         // the warp-specialised kernel with two softmax threads per query row (24 warps)
+  kAttnHelper = 4,           // the warp-specialised kernel whose correction group takes a share of every row
+  kAttnHalfStep = 5,         // warp-specialised, softmax steps of 64 keys in two alternating score buffers per tile
 };
 
 // KIND, D, BLOCK_N, STAGES, POLY are compile-time tuning keys (POLY: how many of every four
@@ -42,6 +45,13 @@ inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, 
     static_assert(POLY >= 0 && POLY <= 2, "split-row kernel: POLY is 0, 1 or 2");
     rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, 0, 2, (POLY == 0 ? 64 : POLY == 1 ? 80 : 96)>(
         q, k, v, o, shp, st, causal, scale, stream);
+  } else if constexpr (KIND == kAttnHelper) {
+    // POLY picks the share: 1 = keys [80,128), 2 = keys [96,128) of every tile go to the helper.
+    static_assert(POLY == 1 || POLY == 2, "helper kernel: POLY is 1 or 2");
+    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, 0, 3, (POLY == 1 ? 80 : 96)>(q, k, v, o, shp, st, causal, scale,
+                                                                                 stream);
+  } else if constexpr (KIND == kAttnHalfStep) {
+    rc = sm100::launch_attn_fwd_wsh<D, STAGES>(q, k, v, o, shp, st, causal, scale, stream);
   } else {
     static_assert(KIND == kAttnPersistent, "unknown kernel kind");
     rc = sm100::launch_attn_fwd_wsp<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);

@@ -31,6 +31,13 @@
 // exponentials on the FMA pipe when KA > 64 (see softmax_part_tile).  Warps 0-7 then serve tile 0,
 // warps 8-15 tile 1, and the correction / MMA / producer warps follow.
 //
+// Helper variant (SPLIT = 3, 16 warps as in the plain kernel): the softmax group of a tile works on
+// keys [0,KA) only, and the correction group, otherwise idle, takes keys [KA,128) of both tiles with
+// its exponentials on the FMA pipe.  It runs on the same schedulers as the softmax warps, so its
+// arithmetic fills the issue slots that the softmax warps leave while they wait for the
+// special-function unit, and a quarter of that unit's work disappears.  The group takes part in
+// the offset decision itself, so the factor for O needs no hand-over: it rescales O right there.
+//
 // Every barrier wait is bounded (see sm100_ptx.cuh): a protocol error ends as a status
 // word and a wrong answer, never as a hung GPU.
 
@@ -48,6 +55,13 @@
 #endif
 #ifndef FRAY_WS_REGS_O
 #define FRAY_WS_REGS_O 64
+#endif
+// Helper variant: the correction group also runs a share of the softmax and needs more registers.
+#ifndef FRAY_WS3_REGS_S
+#define FRAY_WS3_REGS_S 168
+#endif
+#ifndef FRAY_WS3_REGS_C
+#define FRAY_WS3_REGS_C 112
 #endif
 // The same for the split-row variant.  setmaxnreg only moves registers inside the CTA's own
 // allocation (threads x registers at launch = 768 x 80 here, not the whole register file), and an
@@ -67,19 +81,21 @@ namespace sm100 {
 template <int D, int BN, int STAGES, int SPLIT = 1, int KA = 64>
 struct WsCfg {
   static_assert(KA == 64 || KA == 80 || KA == 96, "keys of a tile that the first softmax group of a split row takes");
-  static_assert(SPLIT == 2 || KA == 64, "KA only applies to split rows");
-  static_assert(SPLIT == 1 || SPLIT == 2, "one or two softmax threads per query row");
+  static_assert(SPLIT >= 2 || KA == 64, "KA only applies to split rows");
+  static_assert(SPLIT != 3 || KA > 64, "the helper takes the smaller part");
+  static_assert(SPLIT >= 1 && SPLIT <= 3, "1: one softmax thread per row; 2: two; 3: one plus the correction group as helper");
+  static constexpr bool kHelper = SPLIT == 3;
   static_assert(D == 64 || D == 128, "head dim must be 64 or 128");
   static_assert(BN == 128, "the warp-specialised kernel uses 128-key tiles");
   static_assert(STAGES >= 2 && STAGES <= 8, "2..8 K/V buffers");
   static constexpr int BM = 128;               // rows per query tile
   // P is handed to the MMA warp in this many column chunks; chunk q covers chunk_steps(q) MMAs of 16 keys.
-  static constexpr int kPChunks = (SPLIT == 2 && KA == 80) ? 5 : 4;
+  static constexpr int kPChunks = (SPLIT >= 2 && KA == 80) ? 5 : 4;
   static constexpr int kChunksA = SPLIT == 1 ? 4 : (KA == 64 ? 2 : 3);  // chunks written by the first group
   __host__ __device__ static constexpr int chunk_steps(int q) {
-    return (SPLIT == 2 && KA == 80 && (q == 2 || q == 3)) ? 1 : 2;
+    return (SPLIT >= 2 && KA == 80 && (q == 2 || q == 3)) ? 1 : 2;
   }
-  static constexpr int kSoftmaxWarps = 8 * SPLIT;
+  static constexpr int kSoftmaxWarps = SPLIT == 2 ? 16 : 8;
   static constexpr int kThreads = 32 * (kSoftmaxWarps + 8);
   static constexpr int kPanels = D / 64;       // 64-element (128-byte) column panels
   static constexpr int kQPanelBytes = BM * 128;
@@ -92,7 +108,7 @@ struct WsCfg {
   static constexpr int kNumBars = 2 + 2 * STAGES + 2 * 5 + 2 * kPChunks;
   static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][128], l[2][128]
   static constexpr int kOffXchg = kOffStats + 4 * 128 * 4;  // half-row maxima [2 parities][2 tiles][2 halves][128]
-  static constexpr int kXchgBytes = SPLIT == 2 ? 2 * 2 * 2 * 128 * 4 : 0;
+  static constexpr int kXchgBytes = SPLIT >= 2 ? 2 * 2 * 2 * 128 * 4 : 0;
 #ifdef FRAY_ATTN_TRACE
   static constexpr int kOffTrace = kOffXchg + kXchgBytes;
   static constexpr int kSmemBytes = kOffTrace + 4 * 800 + 1024;
@@ -106,10 +122,11 @@ struct WsCfg {
 #ifdef FRAY_WS2_REGS_A
   static constexpr int kRegsSoftmax = SPLIT == 2 ? FRAY_WS2_REGS_A : FRAY_WS_REGS_S;
 #else
-  static constexpr int kRegsSoftmax = SPLIT == 2 ? (KA == 64 ? 88 : KA == 80 ? 96 : 112) : FRAY_WS_REGS_S;
+  static constexpr int kRegsSoftmax =
+      SPLIT == 2 ? (KA == 64 ? 88 : KA == 80 ? 96 : 112) : SPLIT == 3 ? FRAY_WS3_REGS_S : FRAY_WS_REGS_S;
 #endif
   static constexpr int kRegsSoftmaxB = SPLIT == 2 ? 176 - kRegsSoftmax : kRegsSoftmax;  // second group of a split row
-  static constexpr int kRegsCorrection = SPLIT == 2 ? FRAY_WS2_REGS_C : FRAY_WS_REGS_C;
+  static constexpr int kRegsCorrection = SPLIT == 2 ? FRAY_WS2_REGS_C : SPLIT == 3 ? FRAY_WS3_REGS_C : FRAY_WS_REGS_C;
   static constexpr int kRegsOther = SPLIT == 2 ? FRAY_WS2_REGS_O : FRAY_WS_REGS_O;
   // Registers per thread the CTA is launched with: what __launch_bounds__(kThreads, 1) lets ptxas use.
   static constexpr int kRegsAtLaunch = (65536 / kThreads) / 8 * 8;
@@ -151,7 +168,7 @@ inline int read_attn_trace(unsigned int* out, int max_words) {
 
 
 template <int D, int BN, int STAGES, int POLY, int SPLIT, int KA>
-__global__ void __launch_bounds__(256 + 256 * SPLIT, 1)
+__global__ void __launch_bounds__(SPLIT == 2 ? 768 : 512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                    int num_heads, int seq_len, int causal, float scale_log2) {
@@ -247,7 +264,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int role = warp < Cfg::kSoftmaxWarps ? 0 : warp - Cfg::kSoftmaxWarps + 8;
   if (role < 8) {
     // =============================================================== softmax groups
-    const int i = warp / (4 * SPLIT);     // query tile of this group
+    const int i = warp / (SPLIT == 2 ? 8 : 4);  // query tile of this group
     const int r = tid & 127;              // row inside the tile
     const int n_i = i ? n_t1 : n_t0;
     const int row = m0 + i * Cfg::BM + r;
@@ -281,6 +298,30 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         __syncwarp();
         if (lane == 0) mbar_arrive(corr_ready + i);
       }
+    } else if constexpr (SPLIT == 3) {
+      // Keys [0,KA) of every step; the helper group takes the rest and owns the O rescaling.
+      set_max_regs_inc<Cfg::kRegsSoftmax>();
+      auto ignore_alpha = [](float) {};
+      for (int j = 0; j < n_i; ++j) {
+        FRAY_CRIT_WAIT(s_full + i, j & 1, abort_flag, 0x201 + i, j);
+        tc_fence_after_sync();
+        if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
+        const int kv0 = j * BN;
+        const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+        float* x = xchg + (((j & 1) * 2 + i) * 2) * 128 + r;
+        unsigned int* tr = nullptr;
+#ifdef FRAY_ATTN_TRACE
+        if (trace_on && r == FRAY_TRACE_ROW && j < kTraceIters) tr = trace_sm + i * kTraceIters + j;
+#endif
+        softmax_part_tile<BN, 0, KA, false, 0>(t_s, p_bar, ignore_alpha, x, x + 128, 2 + i, j == 0, need_mask, kv0, row,
+                                               seq_len, causal, scale_log2, lane, m_ref, l_run, tr);
+        if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
+      }
+      if (n_i > 0) {
+        l_buf[i * 128 + r] = l_run;  // partial sum over this group's keys; the helper adds its own
+        __syncwarp();
+        if (lane == 0) mbar_arrive(corr_ready + i);
+      }
     } else {
       // Two groups per tile: the first takes keys [0,KA) of every step, the second keys [KA,128).
       auto part_role = [&](auto part_tag) __attribute__((always_inline)) {
@@ -297,13 +338,18 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (trace_on && r == FRAY_TRACE_ROW && PART == FRAY_TRACE_PART && j < kTraceIters) tr = trace_sm + i * kTraceIters + j;
 #endif
           if constexpr (PART == 0) {
-            softmax_part_tile<BN, 0, KA, false, 0>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, x, x + 128,
-                                                   2 + i, j == 0, need_mask, kv0, row, seq_len, causal, scale_log2,
-                                                   lane, m_ref, l_run, tr);
+            auto publish_alpha = [&](float alpha) {
+              alpha_buf[i * 128 + r] = alpha;
+              __syncwarp();
+              if (lane == 0) mbar_arrive(corr_ready + i);
+            };
+            softmax_part_tile<BN, 0, KA, false, 0>(t_s, p_bar, publish_alpha, x, x + 128, 2 + i, j == 0, need_mask, kv0,
+                                                   row, seq_len, causal, scale_log2, lane, m_ref, l_run, tr);
           } else {
-            softmax_part_tile<BN, KA, BN - KA, (KA > 64), Cfg::kChunksA>(
-                t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, x + 128, x, 2 + i, j == 0, need_mask, kv0, row,
-                seq_len, causal, scale_log2, lane, m_ref, l_run, tr);
+            auto ignore_alpha = [](float) {};
+            softmax_part_tile<BN, KA, BN - KA, (KA > 64), Cfg::kChunksA>(t_s, p_bar, ignore_alpha, x + 128, x, 2 + i,
+                                                                         j == 0, need_mask, kv0, row, seq_len, causal,
+                                                                         scale_log2, lane, m_ref, l_run, tr);
           }
           if (r == FRAY_TRACE_ROW && PART == FRAY_TRACE_PART) FRAY_TRACE(4, i, j);
         }
@@ -336,7 +382,49 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     set_max_regs_dec<Cfg::kRegsCorrection>();
     const int r = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    for (int j = 1; j < n_max; ++j) {
+    float l_help0 = 0.f, l_help1 = 0.f;  // helper variant: row sums over this group's keys
+    if constexpr (Cfg::kHelper) {
+      float m_help0 = -INFINITY, m_help1 = -INFINITY;
+      auto helper_step = [&](auto tile_tag, int j, float& m_ref, float& l_part) __attribute__((always_inline)) {
+        constexpr int i = decltype(tile_tag)::value;
+        FRAY_CRIT_WAIT(s_full + i, j & 1, abort_flag, 0x341 + i, j);
+        tc_fence_after_sync();
+        const int kv0 = j * BN;
+        const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+        const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1) + lane_base;
+        const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1) + lane_base;
+        float* x = xchg + (((j & 1) * 2 + i) * 2) * 128 + r;
+        // Called on every step but the first with this step's factor: rescale O if any row of the
+        // warp moved its offset, then tell the MMA warp that O may be accumulated into.
+        auto rescale_o = [&](float alpha) {
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            mbar_wait(o_full + i, (j - 1) & 1, abort_flag, 0x311 + i, j);
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t orr[32];
+              tmem_ld_x32(t_o + c * 32, orr);
+              tmem_wait_ld();
+#pragma unroll
+              for (int q = 0; q < 32; ++q) orr[q] = __float_as_uint(__uint_as_float(orr[q]) * alpha);
+              tmem_st_x32(t_o + c * 32, orr);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(o_rescaled + i);
+        };
+        softmax_part_tile<BN, KA, BN - KA, true, Cfg::kChunksA>(t_s, p_full + i * Cfg::kPChunks, rescale_o, x + 128, x,
+                                                                 2 + i, j == 0, need_mask, kv0, m0 + i * Cfg::BM + r,
+                                                                 seq_len, causal, scale_log2, lane, m_ref, l_part);
+      };
+      for (int j = 0; j < n_max; ++j) {
+        if (j < n_t0) helper_step(SmInt<0>{}, j, m_help0, l_help0);
+        if (j < n_t1) helper_step(SmInt<1>{}, j, m_help1, l_help1);
+      }
+    }
+    for (int j = 1; j < (Cfg::kHelper ? 0 : n_max); ++j) {
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         if (j < (i ? n_t1 : n_t0)) {
@@ -370,8 +458,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       const int n_i = i ? n_t1 : n_t0;
       if (n_i > 0) {
         const uint32_t ph = (n_i - 1) & 1;
-        mbar_wait(corr_ready + i, ph, abort_flag, 0x321 + i, n_i);
-        const float l = l_buf[i * 128 + r];
+        // corr_ready completes once per published alpha and once for the final row sum; in the helper
+        // variant only the latter happens
+        mbar_wait(corr_ready + i, Cfg::kHelper ? 0u : ph, abort_flag, 0x321 + i, n_i);
+        const float l = l_buf[i * 128 + r] + (Cfg::kHelper ? (i ? l_help1 : l_help0) : 0.f);
         const float inv_l = l > 0.f ? 1.f / l : 1.f;
         mbar_wait(o_full + i, ph, abort_flag, 0x331 + i, n_i);
         tc_fence_after_sync();
@@ -470,7 +560,9 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if ((i == 1) || !(j < n1)) mma_commit_elect(kv_empty + slot);
         FRAY_TRACE(8, i, j);
       };
-      auto issue_pv = [&](int i, int j) __attribute__((always_inline)) {  // O_i (+)= P_i(j) . V_j, chunk by chunk as P arrives
+      // O_i (+)= P_i(j) . V_j, chunk by chunk as P arrives.  (Waiting for the next K tile's barrier here,
+      // ahead of the last chunk, to take that round trip off the path to the next S made no difference.)
+      auto issue_pv = [&](int i, int j) __attribute__((always_inline)) {
         const int t = 2 * j + 1;
         const int slot = t % STAGES;
         mbar_wait(kv_full + slot, (t / STAGES) & 1, abort_flag, 0x502, t);

@@ -259,16 +259,17 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
 // parity) and both meet on the named barrier pair_barrier (256 threads: the two warpgroups of the
 // tile).  That barrier also orders the P stores of the second part (which land in columns below
 // 64) behind the first part's loads of the scores that sit there.  Both threads keep the same
-// m_ref; each keeps the partial row sum of its own keys (the caller adds the two at the end); the
-// first part publishes alpha.
+// m_ref; each keeps the partial row sum of its own keys (the caller adds the two at the end).
+// on_alpha(alpha) is called on every step but a row's first with the factor by which the running
+// state shrinks (1 when the offset stays): the caller publishes it or applies it to O.
 //
 // P is handed over in pieces of 32 keys (16 where a part begins or ends on an odd multiple of 16);
 // piece n of this part arrives on p_bar[CHUNK0 + n].
-template <int BN, int KEY0, int NKEYS, bool USE_POLY, int CHUNK0>
-__device__ __forceinline__ void softmax_part_tile(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
-                                                  float* xchg_mine, const float* xchg_other, int pair_barrier,
-                                                  bool first_tile, bool need_mask, int kv0, int row, int seq_len,
-                                                  int causal, float scale_log2, int lane, float& m_ref, float& l_run,
+template <int BN, int KEY0, int NKEYS, bool USE_POLY, int CHUNK0, class AlphaFn>
+__device__ __forceinline__ void softmax_part_tile(uint32_t t_s, uint64_t* p_bar, AlphaFn&& on_alpha, float* xchg_mine,
+                                                  const float* xchg_other, int pair_barrier, bool first_tile,
+                                                  bool need_mask, int kv0, int row, int seq_len, int causal,
+                                                  float scale_log2, int lane, float& m_ref, float& l_run,
                                                   unsigned int* tr = nullptr) {
   static_assert(BN == 128, "written for 128-key tiles");
   static_assert(KEY0 % 16 == 0 && NKEYS % 16 == 0 && NKEYS >= 32 && KEY0 + NKEYS <= BN, "parts are multiples of 16 keys");
@@ -316,11 +317,7 @@ __device__ __forceinline__ void softmax_part_tile(uint32_t t_s, uint64_t* p_bar,
       l_run *= alpha;
       m_ref = m_new;
     }
-    if constexpr (KEY0 == 0) {
-      *alpha_slot = alpha;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(corr_bar);
-    }
+    on_alpha(alpha);
   }
   const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
 
@@ -390,6 +387,92 @@ __device__ __forceinline__ void softmax_part_tile(uint32_t t_s, uint64_t* p_bar,
     if constexpr (NKEYS == 128) piece(SmInt<96>{}, I32{}, 3);
     if constexpr (NKEYS % 32 == 16) piece(SmInt<NKEYS - 16>{}, I16{}, NKEYS / 32);
   }
+  l_run += (rs0 + rs1) + (rs2 + rs3);
+}
+
+
+// One softmax step over a 64-key score tile (one thread per row), for the kernel that pipelines
+// half tiles: the scores sit in 64 tensor-memory columns starting at t_s, P (fp16) overwrites the
+// first 32 of them and is handed over in one piece (p_bar, one arrival per warp): the P.V product of
+// a step is not what the group waits for next, so an early first chunk buys nothing and a second
+// hand-over costs the group and the MMA warp a barrier round trip each.  Same arithmetic as softmax_tile: base-2 exponentials, lazy offset, row sum from the
+// unrounded values.  alpha is published on every step but a row's first.
+//
+// my_turn / other_turn (both or neither null): the two softmax groups of a CTA take turns on the
+// exponentials.  Their warps share the schedulers, and a step is two kinds of work: loads, row max
+// and hand-over, which leave the special-function unit idle, and the exponentials, which saturate
+// it.  Two groups that run their steps in phase compete for the unit and then leave it idle
+// together; kept in anti-phase, one group's exponentials cover the other's remaining work.  The
+// group waits on my_turn (phase parity turn_parity) before its first exponential and arrives on
+// other_turn (count 4, one arrival per warp) after its last.
+__device__ __forceinline__ void softmax_half_step(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
+                                                  bool first_tile, bool need_mask, int kv0, int row, int seq_len,
+                                                  int causal, float scale_log2, int lane, float& m_ref, float& l_run,
+                                                  uint64_t* my_turn, uint64_t* other_turn, uint32_t turn_parity,
+                                                  volatile uint32_t* abort_flag, unsigned int* tr = nullptr) {
+  uint32_t sc[64];
+  tmem_ld_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sc[0]));
+  tmem_ld_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sc[32]));
+  tmem_wait_ld();
+  FRAY_SM_TRACE(tr, 1);
+  if (need_mask) {
+#pragma unroll
+    for (int c = 0; c < 64; ++c) {
+      const int kv = kv0 + c;
+      if (kv >= seq_len || (causal && kv > row)) sc[c] = __float_as_uint(-INFINITY);
+    }
+  }
+  float mx[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) mx[q] = __uint_as_float(sc[q]);
+#pragma unroll
+  for (int c = 8; c < 64; c += 8) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) mx[q] = fmaxf(mx[q], __uint_as_float(sc[c + q]));
+  }
+  const float m_new = fmaxf(
+      fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7]))), m_ref);
+  if (first_tile) {
+    m_ref = m_new;
+  } else {
+    float alpha = 1.f;
+    if ((m_new - m_ref) * scale_log2 > kRescaleThreshold) {
+      alpha = ex2_approx((m_ref - m_new) * scale_log2);
+      l_run *= alpha;
+      m_ref = m_new;
+    }
+    *alpha_slot = alpha;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(corr_bar);
+  }
+  FRAY_SM_TRACE(tr, 2);
+  const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
+  float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+  uint32_t pk[32];
+  if (my_turn != nullptr) mbar_wait(my_turn, turn_parity, abort_flag, 0xA01, kv0);
+#pragma unroll
+  for (int c = 0; c < 64; c += 4) {
+    const float p0 = ex2_approx(fmaf(__uint_as_float(sc[c]), scale_log2, neg_m));
+    const float p1 = ex2_approx(fmaf(__uint_as_float(sc[c + 1]), scale_log2, neg_m));
+    const float p2 = ex2_approx(fmaf(__uint_as_float(sc[c + 2]), scale_log2, neg_m));
+    const float p3 = ex2_approx(fmaf(__uint_as_float(sc[c + 3]), scale_log2, neg_m));
+    rs0 += p0;
+    rs1 += p1;
+    rs2 += p2;
+    rs3 += p3;
+    pk[c >> 1] = pack_half2(p0, p1);
+    pk[(c >> 1) + 1] = pack_half2(p2, p3);
+  }
+  if (other_turn != nullptr) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(other_turn);
+  }
+  tmem_st_x32(t_s, pk);
+  tmem_wait_st();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(p_bar);
+  FRAY_SM_TRACE(tr, 9);
   l_run += (rs0 + rs1) + (rs2 + rs3);
 }
 

@@ -64,7 +64,7 @@ _RC_TENSOR_MAP = 6
 
 
 def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
-    """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised, 2 persistent, 3 warp-specialised with split rows), KV tile, KV stages, exp2 mix."""
+    """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised, 2 persistent, 3 warp-specialised with split rows, 4 warp-specialised with the correction group helping), KV tile, KV stages, exp2 mix."""
     space = [
         {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # fp32 exponentials
         {"KIND": 0, "BLOCK_N": 128, "STAGES": 1, "POLY": 0},
@@ -87,6 +87,9 @@ EXTRA_VARIANTS = (
     {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 16},  # packed fp16 exponentials: the unit needs two passes for them, no gain
     {"KIND": 3, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # two softmax threads per row, 64 keys each
     {"KIND": 3, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},   # ... 80 keys on the special-function unit, 48 on the polynomial
+    {"KIND": 4, "BLOCK_N": 128, "STAGES": 4, "POLY": 2},   # correction group takes keys [96,128) of every tile on the polynomial
+    {"KIND": 4, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},   # ... keys [80,128)
+    {"KIND": 5, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # softmax steps of 64 keys, two score buffers per tile
 )
 
 
