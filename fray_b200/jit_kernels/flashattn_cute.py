@@ -64,9 +64,15 @@ _RC_TENSOR_MAP = 6
 
 
 def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
-    """Candidate kernels for head dim ``d``: kind (0 single-role, 1 warp-specialised, 2 persistent, 3 warp-specialised with split rows, 4 warp-specialised with the correction group helping), KV tile, KV stages, exp2 mix."""
+    """Candidate kernels for head dim ``d``.
+
+    KIND: 0 single-role, 1 warp-specialised (whole 128-key steps), 2 persistent, 3 split rows, 4 correction
+    group as softmax helper, 5 warp-specialised with 64-key steps; BLOCK_N / STAGES: KV tile and ring depth;
+    POLY: exponential mode of kinds 1-4 (flash_attn/flash_attn_sm100.cuh).
+    """
     space = [
-        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # fp32 exponentials
+        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # warp-specialised, whole 128-key steps
+        {"KIND": 5, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # warp-specialised, 64-key steps in two score buffers (wins on causal shapes)
         {"KIND": 0, "BLOCK_N": 128, "STAGES": 1, "POLY": 0},
         {"KIND": 0, "BLOCK_N": 64, "STAGES": 1, "POLY": 0},
     ]
@@ -89,7 +95,6 @@ EXTRA_VARIANTS = (
     {"KIND": 3, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},   # ... 80 keys on the special-function unit, 48 on the polynomial
     {"KIND": 4, "BLOCK_N": 128, "STAGES": 4, "POLY": 2},   # correction group takes keys [96,128) of every tile on the polynomial
     {"KIND": 4, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},   # ... keys [80,128)
-    {"KIND": 5, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # softmax steps of 64 keys, two score buffers per tile
 )
 
 
