@@ -20,6 +20,10 @@
 // two mbarriers (and two value slots) alternating with the step parity: a single barrier could
 // complete two phases before its consumer looked, and a parity wait cannot tell phase n from n+2.
 //
+// What double buffering does not buy: S(h+1) is issued behind P(h-1).V and so arrives most of a step
+// after P(h-1) was handed over, i.e. late in softmax step h.  Taking the row max of S(h+1) inside
+// step h, under the exponentials, was tried and stalled on exactly that; it would need a third buffer.
+//
 // Issue order in the MMA warp: S0(0) S1(0) S0(1) S1(1) | PV0(h) S0(h+2) PV1(h) S1(h+2) | ...
 // K and V still arrive as 128-key tiles; half step h uses rows 64*(h&1).. of tile h >> 1.
 
@@ -32,10 +36,21 @@ namespace fray {
 namespace sm100 {
 
 // Whether the two softmax groups take turns on the exponentials (-DFRAY_HALFSTEP_TURNS=0/1).
+// Measured 2.5-3.5 % slower than letting them run freely, so off.
 #ifndef FRAY_HALFSTEP_TURNS
-#define FRAY_HALFSTEP_TURNS 1
+#define FRAY_HALFSTEP_TURNS 0
 #endif
 static constexpr bool kHalfStepTurns = FRAY_HALFSTEP_TURNS != 0;
+
+#ifndef FRAY_WSH_REGS_S
+#define FRAY_WSH_REGS_S 184
+#endif
+#ifndef FRAY_WSH_REGS_C
+#define FRAY_WSH_REGS_C 80
+#endif
+#ifndef FRAY_WSH_REGS_O
+#define FRAY_WSH_REGS_O 64
+#endif
 
 template <int D, int STAGES>
 struct WshCfg {
@@ -66,7 +81,8 @@ struct WshCfg {
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
   // register budgets after setmaxnreg: 256*S + 128*C + 128*O = 512*128, the CTA's allocation at launch
-  static constexpr int kRegsSoftmax = 184, kRegsCorrection = 80, kRegsOther = 64;
+  static constexpr int kRegsSoftmax = FRAY_WSH_REGS_S, kRegsCorrection = FRAY_WSH_REGS_C, kRegsOther = FRAY_WSH_REGS_O;
+  static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 65536, "register budgets exceed the CTA's allocation");
 };
 
 template <int D, int STAGES>
@@ -180,6 +196,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     float m_ref = -INFINITY;
     float l_run = 0.f;
     const int h_both = h_t0 < h_t1 ? h_t0 : h_t1;  // half steps that both tiles run: these take turns
+    auto mask_needed = [&](int h) { return (h * BH + BH > seq_len) || (causal && (h * BH + BH - 1 > m0 + i * Cfg::BM)); };
     for (int h = 0; h < h_i; ++h) {
       if (*abort_flag) break;  // a wait gave up somewhere in the CTA: stop touching tensor memory
       const int buf = h & 1;
@@ -187,7 +204,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_after_sync();
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, h);
       const int kv0 = h * BH;
-      const bool need_mask = (kv0 + BH > seq_len) || (causal && (kv0 + BH - 1 > m0 + i * Cfg::BM));
+      const bool need_mask = mask_needed(h);
       unsigned int* tr = nullptr;
 #ifdef FRAY_ATTN_TRACE
 #ifndef FRAY_TRACE_MMA  // with it, events 1, 2, 3, 9 belong to the MMA warp
