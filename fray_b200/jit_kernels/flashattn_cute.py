@@ -227,3 +227,71 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
         _fast_path[fast_key] = (runtime, runtime.raw_launch(), args[4:4 + 3 + 12], sm_scale)
     if out is not Output:
         Output.copy_(out)
+
+
+_host_staging: Dict[Any, Any] = {}
+
+
+def flash_attn_cute_host(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: torch.Tensor, *,
+                         causal: bool = False, scale: Optional[float] = None, chunks: Optional[int] = None,
+                         device: Optional[torch.device] = None) -> None:
+    """``flash_attn_cute`` for operands in pinned HOST memory: result written to the pinned ``Output``.
+
+    No counterpart in the reference (its op asserts CUDA tensors, fray/jit_kernels/flashattn_cute.py:17-20);
+    this is the call a host-side caller of the C ABI makes.  The B*H independent (batch, head) units are cut
+    into ``chunks`` slices (default 8) that move through two sets of device staging buffers on three streams:
+    while slice c is computed, slice c+1 is copied in and slice c-1 is copied out, so the two directions of
+    the host link run at the same time and the kernel hides behind them.  Work is ordered after the current
+    stream's earlier work, and the current stream waits for the last copy-out: as with the device op, the
+    result is valid for work queued on the current stream afterwards (or after a synchronize), not at return.
+    """
+    assert all(t.device.type == "cpu" and t.is_pinned() for t in (Q, K, V, Output)), "operands must be pinned host tensors"
+    assert Q.dim() == 4 and Q.shape == K.shape == V.shape == Output.shape and Q.dtype == torch.half
+    assert all(t.is_contiguous() for t in (Q, K, V, Output)), "host operands must be contiguous"
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    units = Q.shape[0] * Q.shape[1]
+    Q, K, V, Output = (t.view(units, t.shape[2], t.shape[3]) for t in (Q, K, V, Output))
+    n = max(1, min(units, chunks if chunks else 8))
+    bounds = [(units * c) // n for c in range(n + 1)]
+    rows = max(b1 - b0 for b0, b1 in zip(bounds, bounds[1:]))
+    key = (dev, rows, tuple(Q.shape[1:]))
+    st = _host_staging.get(key)
+    if st is None:
+        st = {
+            "bufs": [[torch.empty((rows,) + tuple(Q.shape[1:]), dtype=torch.half, device=dev) for _ in range(4)] for _ in range(2)],
+            "s_in": torch.cuda.Stream(device=dev), "s_out": torch.cuda.Stream(device=dev),
+        }
+        _host_staging.clear()  # one shape at a time: the buffers are as large as the operands' slices
+        _host_staging[key] = st
+    s_in, s_out = st["s_in"], st["s_out"]
+    cur = torch.cuda.current_stream(dev)
+    start = torch.cuda.Event()
+    start.record(cur)
+    s_in.wait_event(start)
+    s_out.wait_event(start)
+    computed = [None, None]   # per buffer set: kernel of the slice that last used it has finished
+    drained = [None, None]    # ... and its result has left the device
+    for c, (b0, b1) in enumerate(zip(bounds, bounds[1:])):
+        dq, dk, dv, do = (t[: b1 - b0] for t in st["bufs"][c & 1])   # [units in slice, S, D]
+        if computed[c & 1] is not None:
+            s_in.wait_event(computed[c & 1])      # inputs of slice c-2 are no longer read
+        with torch.cuda.stream(s_in):
+            dq.copy_(Q[b0:b1], non_blocking=True)
+            dk.copy_(K[b0:b1], non_blocking=True)
+            dv.copy_(V[b0:b1], non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(s_in)
+        cur.wait_event(arrived)
+        if drained[c & 1] is not None:
+            cur.wait_event(drained[c & 1])        # output buffer of slice c-2 has been copied out
+        flash_attn_cute(dq.unsqueeze(0), dk.unsqueeze(0), dv.unsqueeze(0), do.unsqueeze(0), causal=causal, scale=scale)
+        computed[c & 1] = torch.cuda.Event()
+        computed[c & 1].record(cur)
+        s_out.wait_event(computed[c & 1])
+        with torch.cuda.stream(s_out):
+            Output[b0:b1].copy_(do, non_blocking=True)
+            drained[c & 1] = torch.cuda.Event()
+            drained[c & 1].record(s_out)
+    for ev in drained:
+        if ev is not None:
+            cur.wait_event(ev)

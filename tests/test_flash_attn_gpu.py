@@ -242,3 +242,34 @@ def test_causality_at_full_length():
     out2 = run_op(q, k2, v2, causal=True)
     assert torch.equal(out[:, :, :p + 1], out2[:, :, :p + 1])
     assert not torch.equal(out[:, :, p + 1:], out2[:, :, p + 1:])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("chunks", [None, 1, 3, 1000])
+def test_host_buffer_call_matches_device_call(chunks, causal):
+    """flash_attn_cute_host stages pinned host operands through the device in batch slices."""
+    from fray_b200.jit_kernels import flash_attn_cute, flash_attn_cute_host
+    torch.manual_seed(5)
+    B, H, S, D = 5, 4, 384, 128
+    hq, hk, hv = (torch.randn(B, H, S, D, dtype=torch.half).pin_memory() for _ in range(3))
+    hout = torch.zeros(B, H, S, D, dtype=torch.half).pin_memory()
+    for _ in range(2):  # the second call reuses the staging buffers
+        flash_attn_cute_host(hq, hk, hv, hout, causal=causal, chunks=chunks)
+        torch.cuda.synchronize()
+    q, k, v = (t.cuda() for t in (hq, hk, hv))
+    out = torch.zeros_like(q)
+    flash_attn_cute(q, k, v, out, causal=causal)
+    torch.cuda.synchronize()
+    assert torch.equal(hout, out.cpu())  # same kernel, same inputs: bit-identical
+
+
+@pytest.mark.gpu
+def test_host_buffer_call_rejects_pageable_and_device_tensors():
+    from fray_b200.jit_kernels import flash_attn_cute_host
+    t = torch.zeros(1, 1, 128, 64, dtype=torch.half)
+    with pytest.raises(AssertionError):
+        flash_attn_cute_host(t, t, t, t)
+    d = t.cuda()
+    with pytest.raises(AssertionError):
+        flash_attn_cute_host(d, d, d, d)
