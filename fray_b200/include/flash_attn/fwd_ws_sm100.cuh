@@ -119,12 +119,8 @@ struct WsCfg {
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
   // register budgets after setmaxnreg (sum over 16 warps = 64K registers)
-#ifdef FRAY_WS2_REGS_A
-  static constexpr int kRegsSoftmax = SPLIT == 2 ? FRAY_WS2_REGS_A : FRAY_WS_REGS_S;
-#else
   static constexpr int kRegsSoftmax =
       SPLIT == 2 ? (KA == 64 ? 88 : KA == 80 ? 96 : 112) : SPLIT == 3 ? FRAY_WS3_REGS_S : FRAY_WS_REGS_S;
-#endif
   static constexpr int kRegsSoftmaxB = SPLIT == 2 ? 176 - kRegsSoftmax : kRegsSoftmax;  // second group of a split row
   static constexpr int kRegsCorrection = SPLIT == 2 ? FRAY_WS2_REGS_C : SPLIT == 3 ? FRAY_WS3_REGS_C : FRAY_WS_REGS_C;
   static constexpr int kRegsOther = SPLIT == 2 ? FRAY_WS2_REGS_O : FRAY_WS_REGS_O;

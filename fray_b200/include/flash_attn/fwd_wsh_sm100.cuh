@@ -207,9 +207,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const bool need_mask = mask_needed(h);
       unsigned int* tr = nullptr;
 #ifdef FRAY_ATTN_TRACE
-#ifndef FRAY_TRACE_MMA  // with it, events 1, 2, 3, 9 belong to the MMA warp
       if (trace_on && r == FRAY_TRACE_ROW && h < kTraceIters) tr = trace_sm + i * kTraceIters + h;
-#endif
 #endif
       // Tile 0 goes first: its first wait names the parity of the phase before the barrier's first
       // one, which reads as complete; from then on each group waits for the other's previous step.

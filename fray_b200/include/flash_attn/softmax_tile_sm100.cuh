@@ -281,9 +281,7 @@ __device__ __forceinline__ void softmax_part_tile(uint32_t t_s, uint64_t* p_bar,
     if constexpr (NKEYS % 32 == 16) tmem_ld_x16(t_s + KEY0 + kFull, reinterpret_cast<uint32_t(&)[16]>(sc[kFull]));
   }
   tmem_wait_ld();
-#ifndef FRAY_TRACE_ST
   FRAY_SM_TRACE(tr, 1);
-#endif
   if (need_mask) {
 #pragma unroll
     for (int c = 0; c < NKEYS; ++c) {
@@ -302,9 +300,7 @@ __device__ __forceinline__ void softmax_part_tile(uint32_t t_s, uint64_t* p_bar,
   const float m_part =
       fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
   *xchg_mine = m_part;
-#ifndef FRAY_TRACE_ST
   FRAY_SM_TRACE(tr, 3);
-#endif
   named_barrier_sync(pair_barrier, 256);
   FRAY_SM_TRACE(tr, 2);
   const float m_new = fmaxf(fmaxf(m_part, *xchg_other), m_ref);
@@ -354,18 +350,12 @@ __device__ __forceinline__ void softmax_part_tile(uint32_t t_s, uint64_t* p_bar,
       pk[c >> 1] = pack_half2(p0, p1);
       pk[(c >> 1) + 1] = pack_half2(p2, p3);
     }
-#ifdef FRAY_TRACE_ST
-    if (n == 0) FRAY_SM_TRACE(tr, 1);
-#endif
     if constexpr (KEYS == 32) {
       tmem_st_x16(t_s + (KEY0 + OFF) / 2, pk);
     } else {
       tmem_st_x8(t_s + (KEY0 + OFF) / 2, pk);
     }
     tmem_wait_st();
-#ifdef FRAY_TRACE_ST
-    if (n == 0) FRAY_SM_TRACE(tr, 3);
-#endif
     tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(p_bar + CHUNK0 + n);
