@@ -24,36 +24,48 @@ enum AttnKernelKind : int {
 
 // KIND, D, BLOCK_N, STAGES, POLY are compile-time tuning keys (POLY: how many of every four
 // element pairs evaluate exp2 by polynomial instead of the special-function unit; used by the
-// warp-specialised kernel only); everything else is a run-time argument.  `rc` receives an
+// warp-specialised kernel only); everything else is a run-time argument.  K and V have num_kv_heads heads
+// (a divisor of num_heads; query head h uses K/V head h / (num_heads / num_kv_heads)); lse is null or an
+// fp32 [B, H, S] array that receives the log-sum-exp of every query row.  `rc` receives an
 // AttnReturnCode; a non-zero value means nothing was launched.
 template <int KIND, int D, int BLOCK_N, int STAGES, int POLY = 0>
 inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, __half* o, int batch_size,
                              int num_heads, int seq_len, int q_sb, int q_sh, int q_ss, int k_sb, int k_sh, int k_ss,
-                             int v_sb, int v_sh, int v_ss, int o_sb, int o_sh, int o_ss, bool causal, float scale,
-                             cudaStream_t stream, int& rc) {
+                             int v_sb, int v_sh, int v_ss, int o_sb, int o_sh, int o_ss, int num_kv_heads, float* lse,
+                             bool causal, float scale, cudaStream_t stream, int& rc) {
   const AttnShape shp{batch_size, num_heads, seq_len, D};
+  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || (reinterpret_cast<uintptr_t>(lse) & 3u) != 0) {
+    rc = num_kv_heads <= 0 || num_heads % num_kv_heads != 0 ? kAttnBadShape : kAttnBadPointer;
+    return;
+  }
+  const AttnExtras ex{num_heads / num_kv_heads, lse};
   const AttnStrides st[4] = {{q_sb, q_sh, q_ss}, {k_sb, k_sh, k_ss}, {v_sb, v_sh, v_ss}, {o_sb, o_sh, o_ss}};
   rc = validate_attn_args(q, k, v, o, shp, st);
   if (rc != kAttnOk) return;
   if constexpr (KIND == kAttnSimple) {
-    rc = sm100::launch_attn_fwd_simple<D, BLOCK_N>(q, k, v, o, shp, st, causal, scale, stream);
+    rc = sm100::launch_attn_fwd_simple<D, BLOCK_N>(q, k, v, o, shp, st, ex, causal, scale, stream);
   } else if constexpr (KIND == kAttnWarpSpecialized) {
-    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);
+    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, ex, causal, scale, stream);
   } else if constexpr (KIND == kAttnSplitRow) {
     // POLY picks how a row is divided: 0 = 64 + 64 keys, both on the special-function unit;
     // 1 = 80 + 48 and 2 = 96 + 32 keys with the smaller part on the polynomial.
     static_assert(POLY >= 0 && POLY <= 2, "split-row kernel: POLY is 0, 1 or 2");
     rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, 0, 2, (POLY == 0 ? 64 : POLY == 1 ? 80 : 96)>(
-        q, k, v, o, shp, st, causal, scale, stream);
+        q, k, v, o, shp, st, ex, causal, scale, stream);
   } else if constexpr (KIND == kAttnHelper) {
     // POLY picks the share: 1 = keys [80,128), 2 = keys [96,128) of every tile go to the helper.
     static_assert(POLY == 1 || POLY == 2, "helper kernel: POLY is 1 or 2");
-    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, 0, 3, (POLY == 1 ? 80 : 96)>(q, k, v, o, shp, st, causal, scale,
-                                                                                 stream);
+    rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES, 0, 3, (POLY == 1 ? 80 : 96)>(q, k, v, o, shp, st, ex, causal,
+                                                                                 scale, stream);
   } else if constexpr (KIND == kAttnHalfStep) {
-    rc = sm100::launch_attn_fwd_wsh<D, STAGES>(q, k, v, o, shp, st, causal, scale, stream);
+    rc = sm100::launch_attn_fwd_wsh<D, STAGES>(q, k, v, o, shp, st, ex, causal, scale, stream);
   } else {
     static_assert(KIND == kAttnPersistent, "unknown kernel kind");
+    // the persistent variant stays at the reference's feature set
+    if (ex.kv_group != 1 || ex.lse != nullptr) {
+      rc = kAttnUnsupported;
+      return;
+    }
     rc = sm100::launch_attn_fwd_wsp<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);
   }
 }

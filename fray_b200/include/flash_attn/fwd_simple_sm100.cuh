@@ -37,7 +37,8 @@ template <int D, int BN>
 __global__ void __launch_bounds__(128, 1)
 attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, __half* __restrict__ o_ptr, int64_t o_sb,
-                       int64_t o_sh, int64_t o_ss, int num_heads, int seq_len, int causal, float scale_log2) {
+                       int64_t o_sh, int64_t o_ss, int num_heads, int seq_len, int causal, float scale_log2,
+                       int kv_group, float* lse) {
   using Cfg = SimpleCfg<D, BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -117,11 +118,11 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_expect_tx(bar_k, Cfg::kKVBytes);
 #pragma unroll
       for (int p = 0; p < Cfg::kHalves; ++p)
-        tma_load_4d(k_smem + p * Cfg::kKVPanelBytes, &tm_k, bar_k, p * 64, j * BN, h, b);
+        tma_load_4d(k_smem + p * Cfg::kKVPanelBytes, &tm_k, bar_k, p * 64, j * BN, h / kv_group, b);
       mbar_expect_tx(bar_v, Cfg::kKVBytes);
 #pragma unroll
       for (int p = 0; p < Cfg::kHalves; ++p)
-        tma_load_4d(v_smem + p * Cfg::kKVPanelBytes, &tm_v, bar_v, p * 64, j * BN, h, b);
+        tma_load_4d(v_smem + p * Cfg::kKVPanelBytes, &tm_v, bar_v, p * 64, j * BN, h / kv_group, b);
       if (j == 0) mbar_wait(bar_q, 0, abort_flag, 0x101);
       mbar_wait(bar_k, ph, abort_flag, 0x102, j);
       tc_fence_after_sync();
@@ -206,6 +207,9 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
   // Epilogue: O / l -> fp16 -> global, 16 bytes per store.
   const float inv_l = l_run > 0.f ? 1.f / l_run : 1.f;
+  if (lse != nullptr && row < seq_len)
+    lse[(static_cast<size_t>(b) * num_heads + h) * seq_len + row] =
+        l_run > 0.f ? (m_run * scale_log2 + log2f(l_run)) * 0.69314718055994531f : -INFINITY;
   __half* o_row = o_ptr + static_cast<int64_t>(b) * o_sb + static_cast<int64_t>(h) * o_sh +
                   static_cast<int64_t>(row) * o_ss;
 #pragma unroll
@@ -234,14 +238,16 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 // Host launcher for the single-role kernel. Returns an AttnReturnCode.
 template <int D, int BN>
 inline int launch_attn_fwd_simple(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
-                                  const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
+                                  const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
+                                  cudaStream_t stream) {
   using Cfg = SimpleCfg<D, BN>;
+  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, shp.S, shp.D};
   CUtensorMap tm_q, tm_k, tm_v;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
-  rc = cached_attn_tensor_map(&tm_k, k, shp, st[1], BN);
+  rc = cached_attn_tensor_map(&tm_k, k, shp_kv, st[1], BN);
   if (rc != kAttnOk) return rc;
-  rc = cached_attn_tensor_map(&tm_v, v, shp, st[2], BN);
+  rc = cached_attn_tensor_map(&tm_v, v, shp_kv, st[2], BN);
   if (rc != kAttnOk) return rc;
 
   auto kernel = attn_fwd_simple_kernel<D, BN>;
@@ -255,7 +261,7 @@ inline int launch_attn_fwd_simple(const __half* q, const __half* k, const __half
   }
   dim3 grid((shp.S + Cfg::BM - 1) / Cfg::BM, shp.B * shp.H);
   kernel<<<grid, 128, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, o, st[3].b, st[3].h, st[3].s, shp.H, shp.S,
-                                                 causal ? 1 : 0, scale * 1.44269504088896340736f);
+                                                 causal ? 1 : 0, scale * 1.44269504088896340736f, ex.kv_group, ex.lse);
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
   return kAttnOk;
 }

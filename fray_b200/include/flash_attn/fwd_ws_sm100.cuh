@@ -107,7 +107,7 @@ struct WsCfg {
   static constexpr int kOffBars = kOffKV + STAGES * kKVTileBytes;
   static constexpr int kNumBars = 2 + 2 * STAGES + 2 * 5 + 2 * kPChunks;
   static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][128], l[2][128]
-  static constexpr int kOffXchg = kOffStats + 4 * 128 * 4;  // half-row maxima [2 parities][2 tiles][2 halves][128]
+  static constexpr int kOffXchg = kOffStats + 6 * 128 * 4;  // (+ m[2][128]) half-row maxima [2 parities][2 tiles][2 halves][128]
   static constexpr int kXchgBytes = SPLIT >= 2 ? 2 * 2 * 2 * 128 * 4 : 0;
 #ifdef FRAY_ATTN_TRACE
   static constexpr int kOffTrace = kOffXchg + kXchgBytes;
@@ -167,7 +167,7 @@ template <int D, int BN, int STAGES, int POLY, int SPLIT, int KA>
 __global__ void __launch_bounds__(SPLIT == 2 ? 768 : 512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                   int num_heads, int seq_len, int causal, float scale_log2) {
+                   int num_heads, int seq_len, int causal, float scale_log2, int kv_group, float* lse) {
   using Cfg = WsCfg<D, BN, STAGES, SPLIT, KA>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -188,6 +188,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
   float* alpha_buf = reinterpret_cast<float*>(smem + Cfg::kOffStats);  // [2][128]
   float* l_buf = alpha_buf + 256;                                      // [2][128]
+  float* m_buf = l_buf + 256;                                          // [2][128] final exponent offsets (for the LSE output)
   float* xchg = reinterpret_cast<float*>(smem + Cfg::kOffXchg);        // [2][2][2][128], split-row variant only
 
 #ifdef FRAY_ATTN_TRACE
@@ -291,6 +292,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       if (n_i > 0) {
         l_buf[i * 128 + r] = l_run;
+        m_buf[i * 128 + r] = m_ref;
         __syncwarp();
         if (lane == 0) mbar_arrive(corr_ready + i);
       }
@@ -315,6 +317,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
       if (n_i > 0) {
         l_buf[i * 128 + r] = l_run;  // partial sum over this group's keys; the helper adds its own
+        m_buf[i * 128 + r] = m_ref;
         __syncwarp();
         if (lane == 0) mbar_arrive(corr_ready + i);
       }
@@ -356,6 +359,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           named_barrier_sync(2 + i, 256);
           if constexpr (PART == 0) {
             l_buf[i * 128 + r] = l_run + *x;
+            m_buf[i * 128 + r] = m_ref;
             __syncwarp();
             if (lane == 0) mbar_arrive(corr_ready + i);
           }
@@ -459,6 +463,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         mbar_wait(corr_ready + i, Cfg::kHelper ? 0u : ph, abort_flag, 0x321 + i, n_i);
         const float l = l_buf[i * 128 + r] + (Cfg::kHelper ? (i ? l_help1 : l_help0) : 0.f);
         const float inv_l = l > 0.f ? 1.f / l : 1.f;
+        if (lse != nullptr && m0 + i * Cfg::BM + r < seq_len) {
+          // log-sum-exp of the scaled scores in natural units: offset plus log of the row sum
+          const float m = m_buf[i * 128 + r];
+          lse[(static_cast<size_t>(b) * num_heads + h) * seq_len + m0 + i * Cfg::BM + r] =
+              l > 0.f ? (m * scale_log2 + log2f(l)) * 0.69314718055994531f : -INFINITY;
+        }
         mbar_wait(o_full + i, ph, abort_flag, 0x331 + i, n_i);
         tc_fence_after_sync();
         if (r == 0) FRAY_TRACE(6, 1, i);  // last P.V of tile i complete, epilogue starts
@@ -519,7 +529,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 #pragma unroll
         for (int p = 0; p < Cfg::kPanels; ++p)
           tma_load_4d(kv_smem + slot * Cfg::kKVTileBytes + p * Cfg::kKVPanelBytes, tm, kv_full + slot, p * 64,
-                      (t >> 1) * BN, h, b);
+                      (t >> 1) * BN, h / kv_group, b);
         if (t == 0) load_q(1);
       }
     } else if (role == 12) {
@@ -617,14 +627,16 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 // Host launcher for the warp-specialised kernel. Returns an AttnReturnCode.
 template <int D, int BN, int STAGES, int POLY, int SPLIT = 1, int KA = 64>
 inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
-                              const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
+                              const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
+                              cudaStream_t stream) {
   using Cfg = WsCfg<D, BN, STAGES, SPLIT, KA>;
+  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, shp.S, shp.D};
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
-  rc = cached_attn_tensor_map(&tm_k, k, shp, st[1], BN);
+  rc = cached_attn_tensor_map(&tm_k, k, shp_kv, st[1], BN);
   if (rc != kAttnOk) return rc;
-  rc = cached_attn_tensor_map(&tm_v, v, shp, st[2], BN);
+  rc = cached_attn_tensor_map(&tm_v, v, shp_kv, st[2], BN);
   if (rc != kAttnOk) return rc;
   rc = cached_attn_tensor_map(&tm_o, o, shp, st[3], Cfg::BM);
   if (rc != kAttnOk) return rc;
@@ -641,7 +653,7 @@ inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v,
   }
   dim3 grid((shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM), shp.B * shp.H);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,
-                                                           scale * 1.44269504088896340736f);
+                                                           scale * 1.44269504088896340736f, ex.kv_group, ex.lse);
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
   return kAttnOk;
 }

@@ -70,12 +70,12 @@ struct WshCfg {
   static constexpr int kOffBars = kOffKV + STAGES * kKVTileBytes;
   // q_full[2] kv_full[S] kv_empty[S] s_full[2][2] p_full[2][2] o_full[2] corr_ready[2][2] l_ready[2] o_rescaled[2][2] o_final[2]
   static constexpr int kNumBars = 2 + 2 * STAGES + 4 + 4 + 2 + 4 + 2 + 4 + 2 + 2;  // + exp_turn[2]
-  static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][2][128], l[2][128]
+  static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][2][128], l[2][128], m[2][128]
 #ifdef FRAY_ATTN_TRACE
-  static constexpr int kOffTrace = kOffStats + 6 * 128 * 4;
+  static constexpr int kOffTrace = kOffStats + 8 * 128 * 4;
   static constexpr int kSmemBytes = kOffTrace + 4 * 800 + 1024;
 #else
-  static constexpr int kSmemBytes = kOffStats + 6 * 128 * 4 + 1024;  // + alignment slack
+  static constexpr int kSmemBytes = kOffStats + 8 * 128 * 4 + 1024;  // + alignment slack
 #endif
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of one CTA");
   static constexpr int kTmemCols = 512;
@@ -89,7 +89,7 @@ template <int D, int STAGES>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                    int num_heads, int seq_len, int causal, float scale_log2) {
+                    int num_heads, int seq_len, int causal, float scale_log2, int kv_group, float* lse) {
   using Cfg = WshCfg<D, STAGES>;
   constexpr int BN = Cfg::BN, BH = Cfg::BH;
   extern __shared__ uint8_t smem_raw[];
@@ -116,6 +116,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
   float* alpha_buf = reinterpret_cast<float*>(smem + Cfg::kOffStats);  // [2 tiles][2 parities][128]
   float* l_buf = alpha_buf + 512;                                      // [2][128]
+  float* m_buf = l_buf + 256;                                          // [2][128] final exponent offsets (for the LSE output)
 
 #ifdef FRAY_ATTN_TRACE
   unsigned int* trace_sm = reinterpret_cast<unsigned int*>(smem + Cfg::kOffTrace);
@@ -220,6 +221,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
     if (h_i > 0) {
       l_buf[i * 128 + r] = l_run;
+      m_buf[i * 128 + r] = m_ref;
       __syncwarp();
       if (lane == 0) mbar_arrive(l_ready + i);
     }
@@ -265,6 +267,11 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mbar_wait(l_ready + i, 0, abort_flag, 0x721 + i, h_i);
         const float l = l_buf[i * 128 + r];
         const float inv_l = l > 0.f ? 1.f / l : 1.f;
+        if (lse != nullptr && m0 + i * Cfg::BM + r < seq_len) {
+          const float m = m_buf[i * 128 + r];
+          lse[(static_cast<size_t>(b) * num_heads + h_idx) * seq_len + m0 + i * Cfg::BM + r] =
+              l > 0.f ? (m * scale_log2 + log2f(l)) * 0.69314718055994531f : -INFINITY;
+        }
         mbar_wait(o_final + i, 0, abort_flag, 0x731 + i, h_i);
         tc_fence_after_sync();
         if (r == 0) FRAY_TRACE(6, 1, i);
@@ -326,7 +333,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int p = 0; p < Cfg::kPanels; ++p)
           tma_load_4d(kv_smem + slot * Cfg::kKVTileBytes + p * Cfg::kKVPanelBytes, tm, kv_full + slot, p * 64,
-                      (t >> 1) * BN, h_idx, b);
+                      (t >> 1) * BN, h_idx / kv_group, b);
         if (t == 0) load_q(1);
       }
     } else if (warp == 12) {
@@ -449,14 +456,16 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 // Host launcher for the half-step kernel. Returns an AttnReturnCode.
 template <int D, int STAGES>
 inline int launch_attn_fwd_wsh(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
-                               const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
+                               const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
+                               cudaStream_t stream) {
   using Cfg = WshCfg<D, STAGES>;
+  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, shp.S, shp.D};
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
-  rc = cached_attn_tensor_map(&tm_k, k, shp, st[1], Cfg::BN);
+  rc = cached_attn_tensor_map(&tm_k, k, shp_kv, st[1], Cfg::BN);
   if (rc != kAttnOk) return rc;
-  rc = cached_attn_tensor_map(&tm_v, v, shp, st[2], Cfg::BN);
+  rc = cached_attn_tensor_map(&tm_v, v, shp_kv, st[2], Cfg::BN);
   if (rc != kAttnOk) return rc;
   rc = cached_attn_tensor_map(&tm_o, o, shp, st[3], Cfg::BM);
   if (rc != kAttnOk) return rc;
@@ -472,7 +481,7 @@ inline int launch_attn_fwd_wsh(const __half* q, const __half* k, const __half* v
   }
   dim3 grid((shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM), shp.B * shp.H);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,
-                                                           scale * 1.44269504088896340736f);
+                                                           scale * 1.44269504088896340736f, ex.kv_group, ex.lse);
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
   return kAttnOk;
 }

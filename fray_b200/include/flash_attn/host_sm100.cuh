@@ -22,6 +22,7 @@ enum AttnReturnCode : int {
   kAttnTensorMapFailed = 6, // the driver rejected the tensor map (layout not expressible)
   kAttnSmemAttrFailed = 7,  // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed
   kAttnLaunchFailed = 8,    // the launch itself reported an error
+  kAttnUnsupported = 9,     // this kernel kind does not implement grouped K/V heads or the LSE output
 };
 
 // Element strides of one [B,H,S,D] tensor; the D stride is 1 by contract.
@@ -31,6 +32,14 @@ struct AttnStrides {
 
 struct AttnShape {
   int B, H, S, D;
+};
+
+// Optional features.  kv_group: query heads per K/V head (1 = every query head has its own K/V;
+// g > 1 = grouped-query attention, K and V hold H / g heads and query head h reads K/V head h / g).
+// lse: when not null, receives log(sum_j exp(scale * q.k_j)) per query row as fp32 [B, H, S], contiguous.
+struct AttnExtras {
+  int kv_group;
+  float* lse;
 };
 
 inline int validate_attn_args(const void* q, const void* k, const void* v, const void* o, const AttnShape& shp,

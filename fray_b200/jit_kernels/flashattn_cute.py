@@ -3,8 +3,8 @@
 Drop-in for the reference op (fray/jit_kernels/flashattn_cute.py:15-45): four fp16 CUDA
 tensors of identical shape ``[B, H, S, D]``, result stored into ``Output``, launch on
 the current stream, nothing returned.  The 4-positional call behaves as in the
-reference (non-causal, scale ``1/sqrt(D)``); ``causal`` and ``scale`` are keyword-only
-extensions.  Unlike the reference, strided views whose last dimension is contiguous are
+reference (non-causal, scale ``1/sqrt(D)``); ``causal``, ``scale`` and ``lse`` are keyword-only
+extensions, and K / V may carry fewer heads than Q (grouped-query attention).  Unlike the reference, strided views whose last dimension is contiguous are
 consumed and produced through their strides (no hidden copies, and a non-contiguous
 ``Output`` really receives the result).
 """
@@ -25,7 +25,7 @@ fray::flash_attn_sm100<{KIND}, {D}, {BLOCK_N}, {STAGES}, {POLY}>(
     Q, K, V, O, batch_size, num_heads, seq_len,
     q_stride_b, q_stride_h, q_stride_s, k_stride_b, k_stride_h, k_stride_s,
     v_stride_b, v_stride_h, v_stride_s, o_stride_b, o_stride_h, o_stride_s,
-    causal, scale, stream, __return_code);
+    num_kv_heads, Lse, causal, scale, stream, __return_code);
 """
 
 # Exported next to `launch`: blocking read (and optional clear) of the device status words.
@@ -49,6 +49,7 @@ arg_defs = (
     ("Q", torch.half), ("K", torch.half), ("V", torch.half), ("O", torch.half),
     ("batch_size", int), ("num_heads", int), ("seq_len", int),
     *((n, int) for n in _STRIDE_NAMES),
+    ("num_kv_heads", int), ("Lse", torch.float),
     ("causal", bool), ("scale", float), ("stream", torch.cuda.Stream),
 )
 
@@ -59,6 +60,7 @@ _RC_TEXT = {
     1: "bad shape", 2: "null or misaligned pointer", 3: "unsupported stride",
     5: "cuTensorMapEncodeTiled not resolvable", 6: "tensor map rejected by the driver",
     7: "could not raise the dynamic shared memory limit", 8: "kernel launch failed",
+    9: "this kernel kind has no grouped K/V heads or LSE output",
 }
 _RC_TENSOR_MAP = 6
 
@@ -162,28 +164,46 @@ def flash_attn_status(clear: bool = True) -> Tuple[int, int, int, int]:
     return tuple(out)
 
 
+_no_lse: Dict[Any, torch.Tensor] = {}
+
+
 def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: torch.Tensor, *,
-                    causal: bool = False, scale: Optional[float] = None) -> None:
+                    causal: bool = False, scale: Optional[float] = None, lse: Optional[torch.Tensor] = None) -> None:
+    """See the module docstring.  Extensions beyond the reference's call:
+
+    ``K`` and ``V`` may be ``[B, H_kv, S, D]`` with ``H_kv`` a divisor of ``H``: query head ``h`` then attends
+    to K/V head ``h // (H // H_kv)`` (grouped-query / multi-query attention).
+    ``lse``: optional contiguous fp32 CUDA tensor ``[B, H, S]`` that receives ``log(sum_j exp(scale * q_i.k_j))``
+    over the keys row ``i`` may see, the quantity needed to merge partial attention results.
+    """
     global _last_runtime
     fast_key = (Q.shape, Q.stride(), K.shape, K.stride(), V.shape, V.stride(), Output.shape, Output.stride(),
                 Q.dtype, K.dtype, V.dtype, Output.dtype, Q.device, K.device, V.device, Output.device,
-                bool(causal), scale, os.getenv("FRAY_ATTN_FORCE"))
+                bool(causal), scale, os.getenv("FRAY_ATTN_FORCE"),
+                None if lse is None else (lse.shape, lse.stride(), lse.dtype, lse.device))
     hit = _fast_path.get(fast_key)
     if hit is not None:
         runtime, launch, ints, sm_scale = hit
         rc = ctypes.c_int(0)
-        launch(Q.data_ptr(), K.data_ptr(), V.data_ptr(), Output.data_ptr(), *ints, bool(causal), sm_scale,
+        launch(Q.data_ptr(), K.data_ptr(), V.data_ptr(), Output.data_ptr(), *ints,
+               0 if lse is None else lse.data_ptr(), bool(causal), sm_scale,
                torch.cuda.current_stream().cuda_stream, ctypes.byref(rc))
         if rc.value == 0:
             _last_runtime = runtime
             return
         # e.g. a misaligned data pointer this time: let the checked path deal with it
-    assert Q.dim() == 4, "expected [B, H, S, D] tensors"
+    assert Q.dim() == 4 and K.dim() == 4, "expected [B, H, S, D] tensors"
     batch_size, num_heads, seq_len, d = Q.shape
-    assert Q.shape == K.shape == V.shape == Output.shape
+    num_kv_heads = K.shape[1]
+    assert Q.shape == Output.shape and K.shape == V.shape
+    assert K.shape == (batch_size, num_kv_heads, seq_len, d), "K and V must match Q in batch, sequence and head dim"
+    assert num_kv_heads > 0 and num_heads % num_kv_heads == 0, "the number of K/V heads must divide the number of Q heads"
     assert Q.dtype == K.dtype == V.dtype == Output.dtype == torch.half
     assert Q.device.type == "cuda", "flash_attn_cute has no CPU path"
     assert Q.device == K.device == V.device == Output.device
+    if lse is not None:
+        assert lse.dtype == torch.float32 and lse.device == Q.device and lse.is_contiguous()
+        assert lse.shape == (batch_size, num_heads, seq_len), "lse must be [B, H, S]"
     if d not in SUPPORTED_HEAD_DIMS:
         raise ValueError(f"head dim {d} not supported (supported: {SUPPORTED_HEAD_DIMS})")
     if batch_size == 0 or num_heads == 0 or seq_len == 0:
@@ -195,9 +215,16 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
     stream = torch.cuda.current_stream()
     sm_scale = float(scale) if scale is not None else 1.0 / math.sqrt(d)
 
+    lse_arg = lse
+    if lse_arg is None:  # a null pointer for the library: an empty tensor's data pointer is 0
+        lse_arg = _no_lse.get(Q.device)
+        if lse_arg is None:
+            lse_arg = _no_lse[Q.device] = torch.empty(0, dtype=torch.float32, device=Q.device)
+
     def pack(q, k, v, out):
         strides = tuple(int(t.stride(i)) if t.shape[i] > 1 else 8 for t in (q, k, v, out) for i in range(3))
-        return (q, k, v, out, int(batch_size), int(num_heads), int(seq_len), *strides, bool(causal), sm_scale, stream)
+        return (q, k, v, out, int(batch_size), int(num_heads), int(seq_len), *strides, int(num_kv_heads), lse_arg,
+                bool(causal), sm_scale, stream)
 
     args = pack(q, k, v, out)
     runtime = jit_tuner.compile_and_tune(
@@ -224,7 +251,7 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
         raise RuntimeError(f"flash_attn_cute launch failed with code {rc} ({_RC_TEXT.get(rc, 'unknown')})")
     if q is Q and k is K and v is V and out is Output:
         # no copies were needed: remember how to launch this layout directly
-        _fast_path[fast_key] = (runtime, runtime.raw_launch(), args[4:4 + 3 + 12], sm_scale)
+        _fast_path[fast_key] = (runtime, runtime.raw_launch(), args[4:4 + 3 + 12 + 1], sm_scale)
     if out is not Output:
         Output.copy_(out)
 

@@ -119,6 +119,28 @@ def flash_fp16p(q, k, v, causal=False, scale=None, block_n=128):
     return (acc * inv.unsqueeze(-1)).half().reshape(q.shape)
 
 
+def expand_kv_heads(k, v, num_heads):
+    """Grouped-query attention restated as plain attention: K/V head g serves query heads g*r .. g*r+r-1,
+    r = num_heads / K-V heads (the mapping torch's ``enable_gqa`` and the vendored Blackwell kernels use)."""
+    r = num_heads // k.shape[-3]
+    return k.repeat_interleave(r, dim=-3), v.repeat_interleave(r, dim=-3)
+
+
+def lse_fp32(q, k, causal=False, scale=None):
+    """log(sum_j exp(scale * q_i . k_j)) over the keys row i may see, fp32, shape q.shape[:-1]."""
+    S, D = q.shape[-2], q.shape[-1]
+    scale = 1.0 / math.sqrt(D) if scale is None else scale
+    qf, kf = (t.reshape(-1, S, D).float() for t in (q, k))
+    out = torch.empty(qf.shape[0], S)
+    mask = torch.ones(S, S, dtype=torch.bool).tril_() if causal else None
+    for i in range(qf.shape[0]):
+        s = (qf[i] @ kf[i].T) * scale
+        if mask is not None:
+            s.masked_fill_(~mask, float("-inf"))
+        out[i] = torch.logsumexp(s, dim=-1)
+    return out.reshape(q.shape[:-1])
+
+
 def calc_diff(x, y):
     """Same measure as the reference's fray/utils.py:48-52."""
     x, y = x.double(), y.double()

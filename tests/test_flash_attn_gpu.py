@@ -190,9 +190,9 @@ def test_direct_c_abi_call(built_kernels):
         out = torch.zeros_like(q)
         st = [2 * 256 * D, 256 * D, D] * 4
         rc = ctypes.c_int(-1)
-        lib.launch(*(ctypes.c_void_p(t.data_ptr()) for t in (q, k, v, out)), 1, 2, 256, *st, ctypes.c_bool(True),
-                   ctypes.c_float(1.0 / math.sqrt(D)), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
-                   ctypes.byref(rc))
+        lib.launch(*(ctypes.c_void_p(t.data_ptr()) for t in (q, k, v, out)), 1, 2, 256, *st, 2, ctypes.c_void_p(0),
+                   ctypes.c_bool(True), ctypes.c_float(1.0 / math.sqrt(D)),
+                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ctypes.byref(rc))
         assert rc.value == 0
         torch.cuda.synchronize()
         status = (ctypes.c_int * 4)()
@@ -273,3 +273,75 @@ def test_host_buffer_call_rejects_pageable_and_device_tensors():
     d = t.cuda()
     with pytest.raises(AssertionError):
         flash_attn_cute_host(d, d, d, d)
+
+
+# ---------------------------------------------------------------- grouped K/V heads and the LSE output
+# The persistent variant keeps the reference's feature set (return code 9 for either extension).
+def _skip_without_extras(variant):
+    if "KIND=2" in variant.split(","):
+        pytest.skip("the persistent variant implements neither grouped K/V heads nor the LSE output")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("kv_heads", [1, 2, 8])
+def test_grouped_kv_heads(variant, kv_heads, causal):
+    _skip_without_extras(variant)
+    g = torch.Generator().manual_seed(31 + kv_heads)
+    B, H, S, D = 2, 8, 320, 128
+    q = torch.randn(B, H, S, D, generator=g).half().cuda()
+    k, v = (torch.randn(B, kv_heads, S, D, generator=g).half().cuda() for _ in range(2))
+    out = run_op(q, k, v, causal, out=torch.zeros_like(q))
+    ke, ve = ref.expand_kv_heads(k.cpu(), v.cpu(), H)
+    check(out, q, ke, ve, causal)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("S,D", [(77, 64), (512, 128), (1500, 128)])
+def test_lse_output(variant, S, D, causal):
+    from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
+    _skip_without_extras(variant)
+    g = torch.Generator().manual_seed(41)
+    B, H = 2, 3
+    q, k, v = (torch.randn(B, H, S, D, generator=g).half().cuda() for _ in range(3))
+    q[0, 0, :, :] *= 6.0  # one head with a wide score range: offsets move during the row
+    out = torch.zeros_like(q)
+    lse = torch.full((B, H, S), float("nan"), device="cuda")
+    flash_attn_cute(q, k, v, out, causal=causal, lse=lse)
+    torch.cuda.synchronize()
+    assert flash_attn_status()[0] == 0
+    check(out, q, k, v, causal)
+    want = ref.lse_fp32(q.cpu(), k.cpu(), causal)
+    # fp32 accumulation of approximate exponentials: absolute error of a natural logarithm.  The
+    # packed-fp16 exponential variant rounds every term to fp16 first (relative 5e-4 each).
+    tol = 3e-3 if "POLY=16" in variant.split(",") else 2e-4
+    assert (lse.cpu() - want).abs().max().item() <= tol
+    # the same call without lse gives the same attention output
+    out2 = torch.zeros_like(q)
+    flash_attn_cute(q, k, v, out2, causal=causal)
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.gpu
+def test_grouped_heads_with_lse_merge_two_key_halves():
+    """LSE is what merging partial results needs: attention over all keys == merge of two halves."""
+    from fray_b200.jit_kernels import flash_attn_cute
+    g = torch.Generator().manual_seed(43)
+    B, H, Hkv, S, D = 1, 4, 2, 512, 128
+    q = torch.randn(B, H, S, D, generator=g).half().cuda()
+    k, v = (torch.randn(B, Hkv, 2 * S, D, generator=g).half().cuda() for _ in range(2))
+    parts = []
+    for half in range(2):
+        kh, vh = (t[:, :, half * S:(half + 1) * S].contiguous() for t in (k, v))
+        o = torch.zeros_like(q)
+        lse = torch.empty(B, H, S, device="cuda")
+        flash_attn_cute(q, kh, vh, o, lse=lse)
+        parts.append((o.float(), lse))
+    torch.cuda.synchronize()
+    (o0, l0), (o1, l1) = parts
+    w0 = torch.sigmoid(l0 - l1).unsqueeze(-1)
+    merged = o0 * w0 + o1 * (1 - w0)
+    ke, ve = ref.expand_kv_heads(k.cpu(), v.cpu(), H)
+    want = torch.softmax(q.cpu().float() @ ke.float().transpose(-1, -2) / math.sqrt(D), -1) @ ve.float()
+    assert (merged.cpu() - want).abs().max().item() <= MAX_ABS

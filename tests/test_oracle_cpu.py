@@ -1,10 +1,12 @@
 """The CPU oracles agree with each other, with torch attention and with the golden fixtures."""
 import importlib.util
+import math
 import os
 
 import numpy as np
 import pytest
 import torch
+import torch.nn.functional as F
 
 from oracle import attention_ref as ref
 from oracle.c_oracle import attn_fwd_c
@@ -81,3 +83,25 @@ def test_inputs_are_reproducible_per_unit():
 def test_flops_formula():
     assert ref.flops(2, 16, 2048, 128, False) == 4 * 2 * 16 * 2048 * 2048 * 128
     assert ref.flops(4, 32, 4096, 128, True) == 2 * 4 * 32 * 4096 * 4096 * 128
+
+
+def test_expand_kv_heads_matches_torch_grouped_attention():
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(2, 6, 40, 64, generator=g)
+    k, v = (torch.randn(2, 2, 40, 64, generator=g) for _ in range(2))
+    ke, ve = ref.expand_kv_heads(k, v, 6)
+    assert ke.shape == q.shape and torch.equal(ke[:, 4], k[:, 1]) and torch.equal(ke[:, 2], k[:, 0])
+    want = F.scaled_dot_product_attention(q, k, v, enable_gqa=True)
+    assert torch.allclose(ref.attention_fp32(q, ke, ve), want, atol=2e-6)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_lse_reference_against_a_direct_sum(causal):
+    g = torch.Generator().manual_seed(4)
+    q, k = (torch.randn(3, 17, 32, generator=g) for _ in range(2))
+    got = ref.lse_fp32(q, k, causal)
+    s = (q.double() @ k.double().transpose(-1, -2)) / math.sqrt(32)
+    if causal:
+        s = s.masked_fill(~torch.ones(17, 17, dtype=torch.bool).tril(), float("-inf"))
+    want = s.exp().sum(-1).log()
+    assert got.shape == (3, 17) and torch.allclose(got.double(), want, atol=1e-5)
