@@ -28,6 +28,33 @@ CASES = {
 }
 
 
+# Cases for the extensions: grouped K/V heads (torch attention with enable_gqa) and the log-sum-exp
+# output (torch.logsumexp of the scaled, masked scores).  name -> (query heads, K/V heads, S, D, causal)
+EXT_CASES = {
+    "gqa_h8_kv2": (8, 2, 320, 128, False),
+    "gqa_h4_kv1_causal": (4, 1, 200, 64, True),
+}
+
+
+def ext_inputs_for(case):
+    h, h_kv, S, D, causal = EXT_CASES[case]
+    g = torch.Generator().manual_seed(9000 + h * 100 + h_kv)
+    q = torch.randn(1, h, S, D, generator=g).half()
+    k, v = (torch.randn(1, h_kv, S, D, generator=g).half() for _ in range(2))
+    return q, k, v, causal
+
+
+def ext_reference(q, k, v, causal):
+    """(attention output, row log-sum-exp), both fp32, from torch on CPU."""
+    qf, kf, vf = q.float(), k.float(), v.float()
+    out = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, is_causal=causal, enable_gqa=True)
+    r = q.shape[1] // k.shape[1]
+    s = (qf @ kf.repeat_interleave(r, dim=1).transpose(-1, -2)) / q.shape[-1] ** 0.5
+    if causal:
+        s = s.masked_fill(~torch.ones(s.shape[-2:], dtype=torch.bool).tril(), float("-inf"))
+    return out, torch.logsumexp(s, dim=-1)
+
+
 def inputs_for(case):
     ci, units, s_override, causal = CASES[case]
     q, k, v = ref.make_inputs(ci, units)
@@ -44,6 +71,12 @@ def main():
             out = out[:, ::16]  # every 16th query row keeps the file small
         np.save(os.path.join(HERE, f"{case}.npy"), out.numpy().astype(np.float32))
         print(case, tuple(out.shape))
+    for case in EXT_CASES:
+        q, k, v, causal = ext_inputs_for(case)
+        out, lse = ext_reference(q, k, v, causal)
+        np.save(os.path.join(HERE, f"{case}.npy"), out[:, :, ::4].numpy().astype(np.float32))  # every 4th row
+        np.save(os.path.join(HERE, f"{case}_lse.npy"), lse.numpy().astype(np.float32))
+        print(case, tuple(out.shape), tuple(lse.shape))
 
 
 if __name__ == "__main__":

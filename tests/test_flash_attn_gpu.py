@@ -345,3 +345,45 @@ def test_grouped_heads_with_lse_merge_two_key_halves():
     ke, ve = ref.expand_kv_heads(k.cpu(), v.cpu(), H)
     want = torch.softmax(q.cpu().float() @ ke.float().transpose(-1, -2) / math.sqrt(D), -1) @ ve.float()
     assert (merged.cpu() - want).abs().max().item() <= MAX_ABS
+
+
+# ---------------------------------------------------------------- committed golden fixtures
+def _golden():
+    import importlib.util
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(here, "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod, here
+
+
+@pytest.mark.parametrize("case", ["c1_full", "c1_causal", "c2_unit0_rows", "c5_stress_unit3", "ragged_s200_causal"])
+def test_against_golden_fixtures(case):
+    import numpy as np
+    mod, here = _golden()
+    q, k, v, causal = mod.inputs_for(case)           # [units, S, D] on the CPU, regenerated from the seed
+    gold = torch.from_numpy(np.load(os.path.join(here, f"{case}.npy")))
+    out = run_op(*(t.unsqueeze(0).cuda() for t in (q, k, v)), causal)[0].cpu()
+    if case == "c2_unit0_rows":
+        out = out[:, ::16]
+    assert (out.float() - gold).abs().max().item() <= MAX_ABS
+    assert ref.calc_diff(out, gold) <= MAX_DIFF
+
+
+@pytest.mark.parametrize("case", ["gqa_h8_kv2", "gqa_h4_kv1_causal"])
+def test_extensions_against_golden_fixtures(case):
+    import numpy as np
+    from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
+    mod, here = _golden()
+    q, k, v, causal = mod.ext_inputs_for(case)
+    gold = torch.from_numpy(np.load(os.path.join(here, f"{case}.npy")))
+    gold_lse = torch.from_numpy(np.load(os.path.join(here, f"{case}_lse.npy")))
+    q, k, v = (t.cuda() for t in (q, k, v))
+    out = torch.zeros_like(q)
+    lse = torch.zeros(q.shape[:-1], device="cuda")
+    flash_attn_cute(q, k, v, out, causal=causal, lse=lse)
+    torch.cuda.synchronize()
+    assert flash_attn_status()[0] == 0
+    assert (out.cpu()[:, :, ::4].float() - gold).abs().max().item() <= MAX_ABS
+    assert ref.calc_diff(out.cpu()[:, :, ::4], gold) <= MAX_DIFF
+    assert (lse.cpu() - gold_lse).abs().max().item() <= 2e-4

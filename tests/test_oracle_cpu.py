@@ -32,6 +32,18 @@ def test_oracles_match_golden(case):
     assert (c_out.float() - t_out.float()).abs().max() <= 2e-3   # C and torch restatements agree
 
 
+@pytest.mark.parametrize("case", sorted(make_golden.EXT_CASES))
+def test_extension_oracles_match_golden(case):
+    """Grouped K/V heads restated as head expansion, and the LSE reference, against the torch-made fixtures."""
+    q, k, v, causal = make_golden.ext_inputs_for(case)
+    gold = torch.from_numpy(np.load(os.path.join(GOLDEN, f"{case}.npy")))
+    gold_lse = torch.from_numpy(np.load(os.path.join(GOLDEN, f"{case}_lse.npy")))
+    ke, ve = ref.expand_kv_heads(k, v, q.shape[1])
+    assert (ref.attention_fp32(q, ke, ve, causal)[:, :, ::4] - gold).abs().max() < 1e-4
+    assert (ref.flash_fp16p(q, ke, ve, causal)[:, :, ::4].float() - gold).abs().max() <= 1e-2
+    assert (ref.lse_fp32(q, ke, causal) - gold_lse).abs().max() < 1e-4
+
+
 def test_c_oracle_matches_sdpa_fp16():
     q, k, v = ref.make_inputs(0)
     got = attn_fwd_c(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0))[0]
