@@ -29,7 +29,7 @@ enum AttnKernelKind : int {
 // fp32 [B, H, S] array that receives the log-sum-exp of every query row.  `rc` receives an
 // AttnReturnCode; a non-zero value means nothing was launched.
 template <int KIND, int D, int BLOCK_N, int STAGES, int POLY = 0>
-inline void flash_attn_sm100(const __half* q, const __half* k, const __half* v, __half* o, int batch_size,
+inline void flash_attn_sm100(const operand_t* q, const operand_t* k, const operand_t* v, operand_t* o, int batch_size,
                              int num_heads, int seq_len, int q_sb, int q_sh, int q_ss, int k_sb, int k_sh, int k_ss,
                              int v_sb, int v_sh, int v_ss, int o_sb, int o_sh, int o_ss, int num_kv_heads, float* lse,
                              bool causal, float scale, cudaStream_t stream, int& rc) {

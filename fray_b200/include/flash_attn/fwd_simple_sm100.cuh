@@ -36,7 +36,7 @@ struct SimpleCfg {
 template <int D, int BN>
 __global__ void __launch_bounds__(128, 1)
 attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                       const __grid_constant__ CUtensorMap tm_v, __half* __restrict__ o_ptr, int64_t o_sb,
+                       const __grid_constant__ CUtensorMap tm_v, operand_t* __restrict__ o_ptr, int64_t o_sb,
                        int64_t o_sh, int64_t o_ss, int num_heads, int seq_len, int causal, float scale_log2,
                        int kv_group, float* lse) {
   using Cfg = SimpleCfg<D, BN>;
@@ -210,7 +210,7 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   if (lse != nullptr && row < seq_len)
     lse[(static_cast<size_t>(b) * num_heads + h) * seq_len + row] =
         l_run > 0.f ? (m_run * scale_log2 + log2f(l_run)) * 0.69314718055994531f : -INFINITY;
-  __half* o_row = o_ptr + static_cast<int64_t>(b) * o_sb + static_cast<int64_t>(h) * o_sh +
+  operand_t* o_row = o_ptr + static_cast<int64_t>(b) * o_sb + static_cast<int64_t>(h) * o_sh +
                   static_cast<int64_t>(row) * o_ss;
 #pragma unroll
   for (int c = 0; c < D / 32; ++c) {
@@ -237,7 +237,7 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
 // Host launcher for the single-role kernel. Returns an AttnReturnCode.
 template <int D, int BN>
-inline int launch_attn_fwd_simple(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
+inline int launch_attn_fwd_simple(const operand_t* q, const operand_t* k, const operand_t* v, operand_t* o, const AttnShape& shp,
                                   const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
                                   cudaStream_t stream) {
   using Cfg = SimpleCfg<D, BN>;

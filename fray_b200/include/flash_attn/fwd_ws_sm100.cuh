@@ -626,7 +626,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
 // Host launcher for the warp-specialised kernel. Returns an AttnReturnCode.
 template <int D, int BN, int STAGES, int POLY, int SPLIT = 1, int KA = 64>
-inline int launch_attn_fwd_ws(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
+inline int launch_attn_fwd_ws(const operand_t* q, const operand_t* k, const operand_t* v, operand_t* o, const AttnShape& shp,
                               const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
                               cudaStream_t stream) {
   using Cfg = WsCfg<D, BN, STAGES, SPLIT, KA>;

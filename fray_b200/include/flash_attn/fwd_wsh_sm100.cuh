@@ -455,7 +455,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
 // Host launcher for the half-step kernel. Returns an AttnReturnCode.
 template <int D, int STAGES>
-inline int launch_attn_fwd_wsh(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
+inline int launch_attn_fwd_wsh(const operand_t* q, const operand_t* k, const operand_t* v, operand_t* o, const AttnShape& shp,
                                const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
                                cudaStream_t stream) {
   using Cfg = WshCfg<D, STAGES>;

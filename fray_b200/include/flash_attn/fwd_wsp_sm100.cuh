@@ -216,7 +216,7 @@ __device__ __forceinline__ void wsp_tile_step(const WspMmaCtx& c, const WspItem&
 template <int D, int BN, int STAGES, int POLY>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, __half* __restrict__ o_ptr, int64_t o_sb, int64_t o_sh,
+                    const __grid_constant__ CUtensorMap tm_v, operand_t* __restrict__ o_ptr, int64_t o_sb, int64_t o_sh,
                     int64_t o_ss, int num_heads, int seq_len, int causal, float scale_log2, int n_pairs, int n_items) {
   using Cfg = WspCfg<D, BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -382,7 +382,7 @@ attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tc_fence_after_sync();
             if (r == 0) FRAY_TRACE(6, i, item_count);  // epilogue of this tile starts
             const int row0 = w.m0 + i * Cfg::BM + cw * 32;  // first row of this warp
-            __half* o_base = o_ptr + static_cast<int64_t>(w.b) * o_sb + static_cast<int64_t>(w.h) * o_sh;
+            operand_t* o_base = o_ptr + static_cast<int64_t>(w.b) * o_sb + static_cast<int64_t>(w.h) * o_sh;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
               uint32_t orr[32];
@@ -501,7 +501,7 @@ attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
 // Host launcher for the persistent kernel. Returns an AttnReturnCode.
 template <int D, int BN, int STAGES, int POLY>
-inline int launch_attn_fwd_wsp(const __half* q, const __half* k, const __half* v, __half* o, const AttnShape& shp,
+inline int launch_attn_fwd_wsp(const operand_t* q, const operand_t* k, const operand_t* v, operand_t* o, const AttnShape& shp,
                                const AttnStrides (&st)[4], bool causal, float scale, cudaStream_t stream) {
   using Cfg = WspCfg<D, BN, STAGES>;
   static_assert((POLY >= 0 && POLY <= 4) || POLY == kExpPackedHalf, "POLY: 0..4 polynomial pairs of 4, or 16 = packed fp16");

@@ -76,7 +76,7 @@ inline PFN_encodeTiled get_encode_tiled() {
   return fn;
 }
 
-// Tensor map over an fp16 [B,H,S,D] tensor (D contiguous) whose box is
+// Tensor map over a 16-bit (fp16 or bf16, see operand_t) [B,H,S,D] tensor (D contiguous) whose box is
 // `box_rows` sequence positions x 64 head-dim elements (one 128-byte swizzle span).
 inline int make_attn_tensor_map(CUtensorMap* map, const void* base, const AttnShape& shp, const AttnStrides& st,
                                 int box_rows) {
@@ -92,7 +92,7 @@ inline int make_attn_tensor_map(CUtensorMap* map, const void* base, const AttnSh
                            static_cast<cuuint64_t>(sb) * 2};
   cuuint32_t box[4] = {64u, static_cast<cuuint32_t>(box_rows), 1u, 1u};
   cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(map, kOperandIsBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? kAttnOk : kAttnTensorMapFailed;

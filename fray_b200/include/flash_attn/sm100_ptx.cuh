@@ -13,7 +13,21 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// 16-bit operand type of this translation unit: fp16 by default, bf16 when bf16_operands.cuh was
+// included first (the JIT does that for bf16 tensors; every built library has one operand type).
+#ifdef FRAY_ATTN_BF16
+#include <cuda_bf16.h>
+#endif
+
 namespace fray {
+#ifdef FRAY_ATTN_BF16
+using operand_t = __nv_bfloat16;
+static constexpr int kOperandIsBf16 = 1;
+#else
+using operand_t = __half;
+static constexpr int kOperandIsBf16 = 0;
+#endif
+
 namespace sm100 {
 
 // Sticky device status: [0] = first failing site code (0 = healthy), [1] = block x,
@@ -223,10 +237,11 @@ __device__ __forceinline__ uint64_t smem_desc_at(uint64_t desc_template, uint32_
 }
 
 // Instruction descriptor for kind::f16 with fp16 A/B and fp32 accumulation.
-//   bits [4,6) D format (1 = f32), [7,10) A format (0 = f16), [10,13) B format,
+//   bits [4,6) D format (1 = f32), [7,10) A format (0 = f16, 1 = bf16), [10,13) B format,
 //   bit 15 A major (1 = MN), bit 16 B major (1 = MN), [17,23) N >> 3, [24,29) M >> 4.
 __host__ __device__ constexpr uint32_t idesc_f16_f32(int m, int n, bool a_mn_major, bool b_mn_major) {
-  return (1u << 4) | (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
+  return (1u << 4) | (static_cast<uint32_t>(kOperandIsBf16) << 7) | (static_cast<uint32_t>(kOperandIsBf16) << 10) |
+         (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
@@ -475,9 +490,15 @@ __device__ __forceinline__ void ex2_poly_pair(float x0, float x1, float& p0, flo
   p0 = ex2_poly(x0);
   p1 = ex2_poly(x1);
 }
+// Two fp32 values rounded to nearest into a pair of the 16-bit operand type (fp16, or bf16 in a
+// bf16 build), low element first.
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   uint32_t r;
+#ifdef FRAY_ATTN_BF16
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+#else
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+#endif
   return r;
 }
 

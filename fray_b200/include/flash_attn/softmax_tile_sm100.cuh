@@ -88,6 +88,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
                                              uint64_t* my_turn, uint64_t* other_turn, uint32_t turn_parity,
                                              volatile uint32_t* abort_flag) {
   static_assert(BN == 128, "written for 128-key tiles");
+  static_assert(POLY != kExpPackedHalf || !kOperandIsBf16, "the packed exponentials produce fp16");
   constexpr int kChunkCols = BN / kSoftmaxPChunks;  // 32 keys per chunk -> 16 packed fp16 columns
 
   // Register diet: the row is handled as two 64-key halves.  Both are loaded once for the row

@@ -1,4 +1,4 @@
-"""``flash_attn_cute(Q, K, V, Output)`` - fp16 attention forward written in place.
+"""``flash_attn_cute(Q, K, V, Output)`` - fp16 (or bf16) attention forward written in place.
 
 Drop-in for the reference op (fray/jit_kernels/flashattn_cute.py:15-45): four fp16 CUDA
 tensors of identical shape ``[B, H, S, D]``, result stored into ``Output``, launch on
@@ -18,6 +18,9 @@ import torch
 from .tuner import jit_tuner
 
 includes = ('"flash_attn/flash_attn_sm100.cuh"',)
+# bf16 tensors get libraries of their own: this header, sorted ahead of the other one by the generator,
+# switches the operand type of the whole translation unit.
+includes_bf16 = ('"flash_attn/bf16_operands.cuh"', *includes)
 
 template = """
 // Templated args from Python JIT call
@@ -36,6 +39,9 @@ extern "C" EXPORT_API int fray_attn_status(int* out4, int clear) {
 extern "C" EXPORT_API void fray_attn_kernel_info(int* out4) {
     out4[0] = {KIND}; out4[1] = {D}; out4[2] = {BLOCK_N}; out4[3] = {STAGES} + 16 * {POLY};
 }
+extern "C" EXPORT_API int fray_attn_operand_is_bf16(void) {
+    return fray::kOperandIsBf16;
+}
 #ifdef FRAY_ATTN_TRACE
 extern "C" EXPORT_API int fray_attn_trace_read(unsigned int* out, int max_words) {
     return fray::sm100::read_attn_trace(out, max_words);
@@ -52,6 +58,9 @@ arg_defs = (
     ("num_kv_heads", int), ("Lse", torch.float),
     ("causal", bool), ("scale", float), ("stream", torch.cuda.Stream),
 )
+
+# the same argument table with bf16 tensors (the generated `launch` prototype is identical: raw pointers)
+arg_defs_bf16 = tuple((n, torch.bfloat16 if t is torch.half else t) for n, t in arg_defs)
 
 SUPPORTED_HEAD_DIMS = (64, 128)
 
@@ -130,6 +139,10 @@ def prebuild(head_dims=SUPPORTED_HEAD_DIMS, prune: bool = False):
             keys = {"D": d, **point}
             code = generate(includes, arg_defs, cpp_format(template, keys), cpp_format(epilogue, keys))
             paths.append(build("flash_attn_cute", arg_defs, code).path)
+        for point in tuning_space(d):  # bf16 operands: the tuning space only
+            keys = {"D": d, **point}
+            code = generate(includes_bf16, arg_defs_bf16, cpp_format(template, keys), cpp_format(epilogue, keys))
+            paths.append(build("flash_attn_cute", arg_defs_bf16, code).path)
     if prune:
         for entry in os.listdir(get_cache_dir()):
             full = os.path.join(get_cache_dir(), entry)
@@ -173,6 +186,7 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
 
     ``K`` and ``V`` may be ``[B, H_kv, S, D]`` with ``H_kv`` a divisor of ``H``: query head ``h`` then attends
     to K/V head ``h // (H // H_kv)`` (grouped-query / multi-query attention).
+    All four tensors may be bf16 instead of fp16 (P is then rounded to bf16 too; accumulation stays fp32).
     ``lse``: optional contiguous fp32 CUDA tensor ``[B, H, S]`` that receives ``log(sum_j exp(scale * q_i.k_j))``
     over the keys row ``i`` may see, the quantity needed to merge partial attention results.
     """
@@ -198,7 +212,8 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
     assert Q.shape == Output.shape and K.shape == V.shape
     assert K.shape == (batch_size, num_kv_heads, seq_len, d), "K and V must match Q in batch, sequence and head dim"
     assert num_kv_heads > 0 and num_heads % num_kv_heads == 0, "the number of K/V heads must divide the number of Q heads"
-    assert Q.dtype == K.dtype == V.dtype == Output.dtype == torch.half
+    assert Q.dtype == K.dtype == V.dtype == Output.dtype and Q.dtype in (torch.half, torch.bfloat16)
+    bf16 = Q.dtype is torch.bfloat16
     assert Q.device.type == "cuda", "flash_attn_cute has no CPU path"
     assert Q.device == K.device == V.device == Output.device
     if lse is not None:
@@ -230,10 +245,10 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
     runtime = jit_tuner.compile_and_tune(
         name="flash_attn_cute",
         keys={"D": d, "CAUSAL": int(bool(causal)), "CLASS": _seq_class(seq_len, batch_size * num_heads),
-              "FORCED": os.getenv("FRAY_ATTN_FORCE", "")},
+              "FORCED": os.getenv("FRAY_ATTN_FORCE", ""), **({"BF16": 1} if bf16 else {})},
         space=tuning_space(d),
-        includes=includes,
-        arg_defs=arg_defs,
+        includes=includes_bf16 if bf16 else includes,
+        arg_defs=arg_defs_bf16 if bf16 else arg_defs,
         template=template,
         args=args,
         epilogue=epilogue,

@@ -24,7 +24,7 @@ extern "C" {
  * log-sum-exp output, the causal flag and the softmax scale, which the reference fixed to
  * contiguous / num_heads / none / false / 1/sqrt(D).
  *
- * Q, O         fp16 device pointers, 16-byte aligned, logical shape [batch, num_heads, seq, D]
+ * Q, O         fp16 (bf16 in a bf16 library, see fray_attn_operand_is_bf16) device pointers, 16-byte aligned, logical shape [batch, num_heads, seq, D]
  *              where D is the head dim the library was built for (fray_attn_kernel_info).
  * K, V         the same with num_kv_heads heads; num_kv_heads divides num_heads and query
  *              head h reads K/V head h / (num_heads / num_kv_heads).
@@ -54,6 +54,10 @@ int fray_attn_status(int* out4, int clear);
  * share} this library was instantiated with - the template keys the reference keeps only in the source text
  * (fray/jit_kernels/flashattn_cute.py:32-38). */
 void fray_attn_kernel_info(int* out4);
+
+/* 1 when Q, K, V and O of this library are bf16, 0 when they are fp16 (the reference is fp16 only:
+ * fray/jit_kernels/flashattn_cute.py:19 asserts torch.half).  The prototype of `launch` is the same. */
+int fray_attn_operand_is_bf16(void);
 
 #ifdef __cplusplus
 }

@@ -20,7 +20,7 @@ def declared_symbols():
 
 
 def test_header_declares_the_expected_entry_points():
-    assert declared_symbols() == ["fray_attn_kernel_info", "fray_attn_status", "launch"]
+    assert declared_symbols() == ["fray_attn_kernel_info", "fray_attn_operand_is_bf16", "fray_attn_status", "launch"]
 
 
 def test_every_library_exports_every_declared_symbol(built_kernels):
@@ -33,7 +33,8 @@ def test_every_library_exports_every_declared_symbol(built_kernels):
         info = (ctypes.c_int * 4)()
         lib.fray_attn_kernel_info(info)
         assert info[1] in (64, 128) and info[2] in (64, 128)
-        seen.add(tuple(info))
+        assert lib.fray_attn_operand_is_bf16() in (0, 1)
+        seen.add((*info, lib.fray_attn_operand_is_bf16()))
     assert len(seen) == len(built_kernels)  # one library per point of the space
 
 

@@ -186,7 +186,8 @@ def test_direct_c_abi_call(built_kernels):
         info = (ctypes.c_int * 4)()
         lib.fray_attn_kernel_info(info)
         D = info[1]
-        q, k, v = (torch.randn(1, 2, 256, D, generator=g).half().cuda() for _ in range(3))
+        dt = torch.bfloat16 if lib.fray_attn_operand_is_bf16() else torch.half
+        q, k, v = (torch.randn(1, 2, 256, D, generator=g).to(dt).cuda() for _ in range(3))
         out = torch.zeros_like(q)
         st = [2 * 256 * D, 256 * D, D] * 4
         rc = ctypes.c_int(-1)
@@ -387,3 +388,31 @@ def test_extensions_against_golden_fixtures(case):
     assert (out.cpu()[:, :, ::4].float() - gold).abs().max().item() <= MAX_ABS
     assert ref.calc_diff(out.cpu()[:, :, ::4], gold) <= MAX_DIFF
     assert (lse.cpu() - gold_lse).abs().max().item() <= 2e-4
+
+
+# ---------------------------------------------------------------- bf16 operands
+# bf16 keeps 8 significant bits: the output itself is rounded with relative error up to 2^-9 and so
+# is every P; the bounds are the fp16 ones scaled by that ratio (2^-9 / 2^-12 = 8).
+BF16_MAX_ABS = 4e-2
+BF16_MAX_DIFF = 4e-5
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("S,D,kv_heads", [(200, 64, 4), (1024, 128, 4), (640, 128, 2)])
+def test_bf16_operands(S, D, kv_heads, causal):
+    from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
+    g = torch.Generator().manual_seed(51)
+    B, H = 2, 4
+    q = torch.randn(B, H, S, D, generator=g).bfloat16().cuda()
+    k, v = (torch.randn(B, kv_heads, S, D, generator=g).bfloat16().cuda() for _ in range(2))
+    out = torch.zeros_like(q)
+    lse = torch.zeros(B, H, S, device="cuda")
+    flash_attn_cute(q, k, v, out, causal=causal, lse=lse)
+    torch.cuda.synchronize()
+    assert flash_attn_status()[0] == 0 and out.dtype == torch.bfloat16
+    ke, ve = ref.expand_kv_heads(k.cpu(), v.cpu(), H)
+    want16 = ref.sdpa_cpu(q.cpu(), ke, ve, causal)                  # torch bf16 attention
+    want32 = ref.attention_fp32(q.cpu(), ke, ve, causal)
+    assert (out.cpu().float() - want16.float()).abs().max().item() <= BF16_MAX_ABS
+    assert ref.calc_diff(out.cpu(), want32) <= BF16_MAX_DIFF
+    assert (lse.cpu() - ref.lse_fp32(q.cpu(), ke, causal)).abs().max().item() <= 2e-4
