@@ -25,20 +25,22 @@ enum AttnKernelKind : int {
 // KIND, D, BLOCK_N, STAGES, POLY are compile-time tuning keys (POLY: how many of every four
 // element pairs evaluate exp2 by polynomial instead of the special-function unit; used by the
 // warp-specialised kernel only); everything else is a run-time argument.  K and V have num_kv_heads heads
-// (a divisor of num_heads; query head h uses K/V head h / (num_heads / num_kv_heads)); lse is null or an
+// (a divisor of num_heads; query head h uses K/V head h / (num_heads / num_kv_heads)) and seq_len_kv rows
+// (seq_len is the number of queries); lse is null or an
 // fp32 [B, H, S] array that receives the log-sum-exp of every query row.  `rc` receives an
 // AttnReturnCode; a non-zero value means nothing was launched.
 template <int KIND, int D, int BLOCK_N, int STAGES, int POLY = 0>
 inline void flash_attn_sm100(const operand_t* q, const operand_t* k, const operand_t* v, operand_t* o, int batch_size,
                              int num_heads, int seq_len, int q_sb, int q_sh, int q_ss, int k_sb, int k_sh, int k_ss,
-                             int v_sb, int v_sh, int v_ss, int o_sb, int o_sh, int o_ss, int num_kv_heads, float* lse,
-                             bool causal, float scale, cudaStream_t stream, int& rc) {
+                             int v_sb, int v_sh, int v_ss, int o_sb, int o_sh, int o_ss, int num_kv_heads,
+                             int seq_len_kv, float* lse, bool causal, float scale, cudaStream_t stream, int& rc) {
   const AttnShape shp{batch_size, num_heads, seq_len, D};
-  if (num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || (reinterpret_cast<uintptr_t>(lse) & 3u) != 0) {
-    rc = num_kv_heads <= 0 || num_heads % num_kv_heads != 0 ? kAttnBadShape : kAttnBadPointer;
+  const bool bad_shape = num_kv_heads <= 0 || num_heads % num_kv_heads != 0 || seq_len_kv <= 0;
+  if (bad_shape || (reinterpret_cast<uintptr_t>(lse) & 3u) != 0) {
+    rc = bad_shape ? kAttnBadShape : kAttnBadPointer;
     return;
   }
-  const AttnExtras ex{num_heads / num_kv_heads, lse};
+  const AttnExtras ex{num_heads / num_kv_heads, lse, seq_len_kv};
   const AttnStrides st[4] = {{q_sb, q_sh, q_ss}, {k_sb, k_sh, k_ss}, {v_sb, v_sh, v_ss}, {o_sb, o_sh, o_ss}};
   rc = validate_attn_args(q, k, v, o, shp, st);
   if (rc != kAttnOk) return;
@@ -62,7 +64,7 @@ inline void flash_attn_sm100(const operand_t* q, const operand_t* k, const opera
   } else {
     static_assert(KIND == kAttnPersistent, "unknown kernel kind");
     // the persistent variant stays at the reference's feature set
-    if (ex.kv_group != 1 || ex.lse != nullptr) {
+    if (ex.kv_group != 1 || ex.lse != nullptr || ex.seq_k != seq_len) {
       rc = kAttnUnsupported;
       return;
     }

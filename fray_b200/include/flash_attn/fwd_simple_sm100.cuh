@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(128, 1)
 attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, operand_t* __restrict__ o_ptr, int64_t o_sb,
                        int64_t o_sh, int64_t o_ss, int num_heads, int seq_len, int causal, float scale_log2,
-                       int kv_group, float* lse) {
+                       int kv_group, float* lse, int seq_k) {
   using Cfg = SimpleCfg<D, BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -91,7 +91,7 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const uint32_t t_s = tmem_base + Cfg::kColS;
   const uint32_t t_o = tmem_base + Cfg::kColO;
 
-  int n_tiles = (seq_len + BN - 1) / BN;
+  int n_tiles = (seq_k + BN - 1) / BN;  // seq_len counts queries, seq_k keys
   if (causal) {
     const int lim = (m0 + Cfg::BM + BN - 1) / BN;
     n_tiles = lim < n_tiles ? lim : n_tiles;
@@ -146,12 +146,12 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     tmem_wait_ld();
 
     const int kv0 = j * BN;
-    const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0));
+    const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0));
     if (need_mask) {
 #pragma unroll
       for (int c = 0; c < BN; ++c) {
         const int kv = kv0 + c;
-        if (kv >= seq_len || (causal && kv > row)) sr[c] = __float_as_uint(-INFINITY);
+        if (kv >= seq_k || (causal && kv > row)) sr[c] = __float_as_uint(-INFINITY);
       }
     }
     float mx = -INFINITY;
@@ -241,7 +241,7 @@ inline int launch_attn_fwd_simple(const operand_t* q, const operand_t* k, const 
                                   const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
                                   cudaStream_t stream) {
   using Cfg = SimpleCfg<D, BN>;
-  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, shp.S, shp.D};
+  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, ex.seq_k, shp.D};
   CUtensorMap tm_q, tm_k, tm_v;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
@@ -261,7 +261,7 @@ inline int launch_attn_fwd_simple(const operand_t* q, const operand_t* k, const 
   }
   dim3 grid((shp.S + Cfg::BM - 1) / Cfg::BM, shp.B * shp.H);
   kernel<<<grid, 128, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, o, st[3].b, st[3].h, st[3].s, shp.H, shp.S,
-                                                 causal ? 1 : 0, scale * 1.44269504088896340736f, ex.kv_group, ex.lse);
+                                                 causal ? 1 : 0, scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k);
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
   return kAttnOk;
 }

@@ -167,7 +167,7 @@ template <int D, int BN, int STAGES, int POLY, int SPLIT, int KA>
 __global__ void __launch_bounds__(SPLIT == 2 ? 768 : 512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                   int num_heads, int seq_len, int causal, float scale_log2, int kv_group, float* lse) {
+                   int num_heads, int seq_len, int causal, float scale_log2, int kv_group, float* lse, int seq_k) {
   using Cfg = WsCfg<D, BN, STAGES, SPLIT, KA>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -205,7 +205,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int h = bh - b * num_heads;
 
   // Number of KV tiles each query tile consumes (0 = tile lies past the end of the sequence).
-  const int n_kv = (seq_len + BN - 1) / BN;
+  const int n_kv = (seq_k + BN - 1) / BN;  // seq_len counts queries, seq_k keys
   auto tiles_for = [&](int i) {
     const int row0 = m0 + i * Cfg::BM;
     int n = row0 < seq_len ? n_kv : 0;
@@ -281,12 +281,12 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
 
         const int kv0 = j * BN;
-        const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+        const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
         // Steps both tiles run take turns on the special-function unit; tile 0 goes first (its first
         // wait uses the parity of the phase "before" the barrier's first one, which reads as complete).
         const bool take_turns = kSfuTurns && j < n_both;
         softmax_tile<BN, POLY>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, need_mask, kv0, row,
-                               seq_len, causal, scale_log2, lane, m_ref, l_run, take_turns ? sfu_turn + i : nullptr,
+                               seq_k, causal, scale_log2, lane, m_ref, l_run, take_turns ? sfu_turn + i : nullptr,
                                take_turns ? sfu_turn + (1 - i) : nullptr, (j + 1 - i) & 1, abort_flag);
         if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
       }
@@ -305,14 +305,14 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         tc_fence_after_sync();
         if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
         const int kv0 = j * BN;
-        const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+        const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
         float* x = xchg + (((j & 1) * 2 + i) * 2) * 128 + r;
         unsigned int* tr = nullptr;
 #ifdef FRAY_ATTN_TRACE
         if (trace_on && r == FRAY_TRACE_ROW && j < kTraceIters) tr = trace_sm + i * kTraceIters + j;
 #endif
         softmax_part_tile<BN, 0, KA, false, 0>(t_s, p_bar, ignore_alpha, x, x + 128, 2 + i, j == 0, need_mask, kv0, row,
-                                               seq_len, causal, scale_log2, lane, m_ref, l_run, tr);
+                                               seq_k, causal, scale_log2, lane, m_ref, l_run, tr);
         if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
       }
       if (n_i > 0) {
@@ -330,7 +330,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           tc_fence_after_sync();
           if (r == FRAY_TRACE_ROW && PART == FRAY_TRACE_PART) FRAY_TRACE(0, i, j);
           const int kv0 = j * BN;
-          const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+          const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
           float* x = xchg + (((j & 1) * 2 + i) * 2) * 128 + r;
           unsigned int* tr = nullptr;
 #ifdef FRAY_ATTN_TRACE
@@ -343,11 +343,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
               if (lane == 0) mbar_arrive(corr_ready + i);
             };
             softmax_part_tile<BN, 0, KA, false, 0>(t_s, p_bar, publish_alpha, x, x + 128, 2 + i, j == 0, need_mask, kv0,
-                                                   row, seq_len, causal, scale_log2, lane, m_ref, l_run, tr);
+                                                   row, seq_k, causal, scale_log2, lane, m_ref, l_run, tr);
           } else {
             auto ignore_alpha = [](float) {};
             softmax_part_tile<BN, KA, BN - KA, (KA > 64), Cfg::kChunksA>(t_s, p_bar, ignore_alpha, x + 128, x, 2 + i,
-                                                                         j == 0, need_mask, kv0, row, seq_len, causal,
+                                                                         j == 0, need_mask, kv0, row, seq_k, causal,
                                                                          scale_log2, lane, m_ref, l_run, tr);
           }
           if (r == FRAY_TRACE_ROW && PART == FRAY_TRACE_PART) FRAY_TRACE(4, i, j);
@@ -390,7 +390,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         FRAY_CRIT_WAIT(s_full + i, j & 1, abort_flag, 0x341 + i, j);
         tc_fence_after_sync();
         const int kv0 = j * BN;
-        const bool need_mask = (kv0 + BN > seq_len) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+        const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
         const uint32_t t_s = tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1) + lane_base;
         const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1) + lane_base;
         float* x = xchg + (((j & 1) * 2 + i) * 2) * 128 + r;
@@ -417,7 +417,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         };
         softmax_part_tile<BN, KA, BN - KA, true, Cfg::kChunksA>(t_s, p_full + i * Cfg::kPChunks, rescale_o, x + 128, x,
                                                                  2 + i, j == 0, need_mask, kv0, m0 + i * Cfg::BM + r,
-                                                                 seq_len, causal, scale_log2, lane, m_ref, l_part);
+                                                                 seq_k, causal, scale_log2, lane, m_ref, l_part);
       };
       for (int j = 0; j < n_max; ++j) {
         if (j < n_t0) helper_step(SmInt<0>{}, j, m_help0, l_help0);
@@ -630,7 +630,7 @@ inline int launch_attn_fwd_ws(const operand_t* q, const operand_t* k, const oper
                               const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
                               cudaStream_t stream) {
   using Cfg = WsCfg<D, BN, STAGES, SPLIT, KA>;
-  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, shp.S, shp.D};
+  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, ex.seq_k, shp.D};
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
@@ -653,7 +653,7 @@ inline int launch_attn_fwd_ws(const operand_t* q, const operand_t* k, const oper
   }
   dim3 grid((shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM), shp.B * shp.H);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,
-                                                           scale * 1.44269504088896340736f, ex.kv_group, ex.lse);
+                                                           scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k);
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
   return kAttnOk;
 }

@@ -89,7 +89,7 @@ template <int D, int STAGES>
 __global__ void __launch_bounds__(512, 1)
 attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                    int num_heads, int seq_len, int causal, float scale_log2, int kv_group, float* lse) {
+                    int num_heads, int seq_len, int causal, float scale_log2, int kv_group, float* lse, int seq_k) {
   using Cfg = WshCfg<D, STAGES>;
   constexpr int BN = Cfg::BN, BH = Cfg::BH;
   extern __shared__ uint8_t smem_raw[];
@@ -132,7 +132,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int h_idx = bh - b * num_heads;
 
   // Number of 128-key K/V tiles each query tile consumes (0 = tile lies past the end of the sequence).
-  const int n_kv = (seq_len + BN - 1) / BN;
+  const int n_kv = (seq_k + BN - 1) / BN;  // seq_len counts queries, seq_k keys
   auto tiles_for = [&](int i) {
     const int row0 = m0 + i * Cfg::BM;
     int n = row0 < seq_len ? n_kv : 0;
@@ -197,7 +197,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     float m_ref = -INFINITY;
     float l_run = 0.f;
     const int h_both = h_t0 < h_t1 ? h_t0 : h_t1;  // half steps that both tiles run: these take turns
-    auto mask_needed = [&](int h) { return (h * BH + BH > seq_len) || (causal && (h * BH + BH - 1 > m0 + i * Cfg::BM)); };
+    auto mask_needed = [&](int h) { return (h * BH + BH > seq_k) || (causal && (h * BH + BH - 1 > m0 + i * Cfg::BM)); };
     for (int h = 0; h < h_i; ++h) {
       if (*abort_flag) break;  // a wait gave up somewhere in the CTA: stop touching tensor memory
       const int buf = h & 1;
@@ -214,7 +214,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // one, which reads as complete; from then on each group waits for the other's previous step.
       const bool turns = kHalfStepTurns && h < h_both;
       softmax_half_step(t_tile + buf * BH, p_full + i * 2 + buf, corr_ready + i * 2 + buf,
-                        alpha_buf + (i * 2 + buf) * 128 + r, h == 0, need_mask, kv0, row, seq_len, causal, scale_log2,
+                        alpha_buf + (i * 2 + buf) * 128 + r, h == 0, need_mask, kv0, row, seq_k, causal, scale_log2,
                         lane, m_ref, l_run, turns ? exp_turn + i : nullptr, turns ? exp_turn + (1 - i) : nullptr,
                         (h + 1 - i) & 1, abort_flag, tr);
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, h);
@@ -459,7 +459,7 @@ inline int launch_attn_fwd_wsh(const operand_t* q, const operand_t* k, const ope
                                const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
                                cudaStream_t stream) {
   using Cfg = WshCfg<D, STAGES>;
-  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, shp.S, shp.D};
+  const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, ex.seq_k, shp.D};
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
   if (rc != kAttnOk) return rc;
@@ -481,7 +481,7 @@ inline int launch_attn_fwd_wsh(const operand_t* q, const operand_t* k, const ope
   }
   dim3 grid((shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM), shp.B * shp.H);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,
-                                                           scale * 1.44269504088896340736f, ex.kv_group, ex.lse);
+                                                           scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k);
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
   return kAttnOk;
 }

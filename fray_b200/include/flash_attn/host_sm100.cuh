@@ -37,9 +37,12 @@ struct AttnShape {
 // Optional features.  kv_group: query heads per K/V head (1 = every query head has its own K/V;
 // g > 1 = grouped-query attention, K and V hold H / g heads and query head h reads K/V head h / g).
 // lse: when not null, receives log(sum_j exp(scale * q.k_j)) per query row as fp32 [B, H, S], contiguous.
+// seq_k: number of keys (K/V rows); the shape's S is the number of queries.  With a causal mask and
+// seq_k != S, query i sees keys 0..i (the mask is aligned to the top left corner, as in torch attention).
 struct AttnExtras {
   int kv_group;
   float* lse;
+  int seq_k;
 };
 
 inline int validate_attn_args(const void* q, const void* k, const void* v, const void* o, const AttnShape& shp,

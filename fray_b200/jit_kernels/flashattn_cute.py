@@ -28,7 +28,7 @@ fray::flash_attn_sm100<{KIND}, {D}, {BLOCK_N}, {STAGES}, {POLY}>(
     Q, K, V, O, batch_size, num_heads, seq_len,
     q_stride_b, q_stride_h, q_stride_s, k_stride_b, k_stride_h, k_stride_s,
     v_stride_b, v_stride_h, v_stride_s, o_stride_b, o_stride_h, o_stride_s,
-    num_kv_heads, Lse, causal, scale, stream, __return_code);
+    num_kv_heads, seq_len_kv, Lse, causal, scale, stream, __return_code);
 """
 
 # Exported next to `launch`: blocking read (and optional clear) of the device status words.
@@ -55,7 +55,7 @@ arg_defs = (
     ("Q", torch.half), ("K", torch.half), ("V", torch.half), ("O", torch.half),
     ("batch_size", int), ("num_heads", int), ("seq_len", int),
     *((n, int) for n in _STRIDE_NAMES),
-    ("num_kv_heads", int), ("Lse", torch.float),
+    ("num_kv_heads", int), ("seq_len_kv", int), ("Lse", torch.float),
     ("causal", bool), ("scale", float), ("stream", torch.cuda.Stream),
 )
 
@@ -184,8 +184,10 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
                     causal: bool = False, scale: Optional[float] = None, lse: Optional[torch.Tensor] = None) -> None:
     """See the module docstring.  Extensions beyond the reference's call:
 
-    ``K`` and ``V`` may be ``[B, H_kv, S, D]`` with ``H_kv`` a divisor of ``H``: query head ``h`` then attends
-    to K/V head ``h // (H // H_kv)`` (grouped-query / multi-query attention).
+    ``K`` and ``V`` may be ``[B, H_kv, S_k, D]`` with ``H_kv`` a divisor of ``H``: query head ``h`` then attends
+    to K/V head ``h // (H // H_kv)`` (grouped-query / multi-query attention), and ``S_k`` may differ from the
+    number of queries (cross attention, or new queries against a longer cache); with ``causal`` query ``i``
+    sees keys ``0..i``, the top-left alignment of torch's ``is_causal``.
     All four tensors may be bf16 instead of fp16 (P is then rounded to bf16 too; accumulation stays fp32).
     ``lse``: optional contiguous fp32 CUDA tensor ``[B, H, S]`` that receives ``log(sum_j exp(scale * q_i.k_j))``
     over the keys row ``i`` may see, the quantity needed to merge partial attention results.
@@ -210,7 +212,8 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
     batch_size, num_heads, seq_len, d = Q.shape
     num_kv_heads = K.shape[1]
     assert Q.shape == Output.shape and K.shape == V.shape
-    assert K.shape == (batch_size, num_kv_heads, seq_len, d), "K and V must match Q in batch, sequence and head dim"
+    seq_len_kv = K.shape[2]
+    assert K.shape == (batch_size, num_kv_heads, seq_len_kv, d), "K and V must match Q in batch and head dim"
     assert num_kv_heads > 0 and num_heads % num_kv_heads == 0, "the number of K/V heads must divide the number of Q heads"
     assert Q.dtype == K.dtype == V.dtype == Output.dtype and Q.dtype in (torch.half, torch.bfloat16)
     bf16 = Q.dtype is torch.bfloat16
@@ -223,6 +226,7 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
         raise ValueError(f"head dim {d} not supported (supported: {SUPPORTED_HEAD_DIMS})")
     if batch_size == 0 or num_heads == 0 or seq_len == 0:
         return
+    assert seq_len_kv > 0, "attention over zero keys is undefined"
 
     q, k, v = (t if _usable_strides(t) else t.contiguous() for t in (Q, K, V))
     out = Output if _usable_strides(Output) else torch.empty_like(Output, memory_format=torch.contiguous_format)
@@ -238,13 +242,13 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
 
     def pack(q, k, v, out):
         strides = tuple(int(t.stride(i)) if t.shape[i] > 1 else 8 for t in (q, k, v, out) for i in range(3))
-        return (q, k, v, out, int(batch_size), int(num_heads), int(seq_len), *strides, int(num_kv_heads), lse_arg,
-                bool(causal), sm_scale, stream)
+        return (q, k, v, out, int(batch_size), int(num_heads), int(seq_len), *strides, int(num_kv_heads),
+                int(seq_len_kv), lse_arg, bool(causal), sm_scale, stream)
 
     args = pack(q, k, v, out)
     runtime = jit_tuner.compile_and_tune(
         name="flash_attn_cute",
-        keys={"D": d, "CAUSAL": int(bool(causal)), "CLASS": _seq_class(seq_len, batch_size * num_heads),
+        keys={"D": d, "CAUSAL": int(bool(causal)), "CLASS": _seq_class(max(seq_len, seq_len_kv), batch_size * num_heads),
               "FORCED": os.getenv("FRAY_ATTN_FORCE", ""), **({"BF16": 1} if bf16 else {})},
         space=tuning_space(d),
         includes=includes_bf16 if bf16 else includes,
@@ -266,7 +270,7 @@ def flash_attn_cute(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, Output: t
         raise RuntimeError(f"flash_attn_cute launch failed with code {rc} ({_RC_TEXT.get(rc, 'unknown')})")
     if q is Q and k is K and v is V and out is Output:
         # no copies were needed: remember how to launch this layout directly
-        _fast_path[fast_key] = (runtime, runtime.raw_launch(), args[4:4 + 3 + 12 + 1], sm_scale)
+        _fast_path[fast_key] = (runtime, runtime.raw_launch(), args[4:4 + 3 + 12 + 2], sm_scale)
     if out is not Output:
         Output.copy_(out)
 

@@ -20,14 +20,16 @@ extern "C" {
  *                  int seq_len, void* stream, int& __return_code)
  * generated for fray::flash_attn_cute<R,C,D> (fray/include/flash_attn/flashattn_cute.cuh:166-239).
  * Added over the reference prototype: element strides of the batch, head and sequence
- * modes of each tensor (the head-dim stride is 1), the number of K/V heads, an optional
+ * modes of each tensor (the head-dim stride is 1), the number of K/V heads and rows, an optional
  * log-sum-exp output, the causal flag and the softmax scale, which the reference fixed to
  * contiguous / num_heads / none / false / 1/sqrt(D).
  *
  * Q, O         fp16 (bf16 in a bf16 library, see fray_attn_operand_is_bf16) device pointers, 16-byte aligned, logical shape [batch, num_heads, seq, D]
  *              where D is the head dim the library was built for (fray_attn_kernel_info).
- * K, V         the same with num_kv_heads heads; num_kv_heads divides num_heads and query
- *              head h reads K/V head h / (num_heads / num_kv_heads).
+ * K, V         the same with num_kv_heads heads and seq_len_kv rows; num_kv_heads divides
+ *              num_heads and query head h reads K/V head h / (num_heads / num_kv_heads).
+ *              seq_len counts the queries (rows of Q, O and Lse).  With causal != 0 query i
+ *              sees keys 0..i whatever the two lengths are.
  * *_stride_*   in elements, positive multiples of 8 (ignored for modes of extent 1).
  * Lse          null, or a 4-byte aligned device pointer to fp32 [batch, num_heads, seq]
  *              (contiguous) that receives log(sum_j exp(scale * q_i . k_j)) of every row.
@@ -40,7 +42,8 @@ extern "C" {
 void launch(void* Q, void* K, void* V, void* O, int batch_size, int num_heads, int seq_len,
             int q_stride_b, int q_stride_h, int q_stride_s, int k_stride_b, int k_stride_h, int k_stride_s,
             int v_stride_b, int v_stride_h, int v_stride_s, int o_stride_b, int o_stride_h, int o_stride_s,
-            int num_kv_heads, void* Lse, bool causal, float scale, void* stream, int* __return_code);
+            int num_kv_heads, int seq_len_kv, void* Lse, bool causal, float scale, void* stream,
+            int* __return_code);
 
 /* Blocking read of the sticky device status: out4[0] is 0 when healthy, else the code of
  * the first in-kernel wait that ran out; out4[1..3] are block x, block y and an iteration

@@ -38,11 +38,11 @@ def test_every_library_exports_every_declared_symbol(built_kernels):
     assert len(seen) == len(built_kernels)  # one library per point of the space
 
 
-def _call(lib, q=0x1000, k=0x1000, v=0x1000, o=0x1000, B=1, H=1, S=128, strides=None, kv_heads=None, lse=0):
+def _call(lib, q=0x1000, k=0x1000, v=0x1000, o=0x1000, B=1, H=1, S=128, strides=None, kv_heads=None, lse=0, Sk=None):
     strides = strides or [8192, 8192, 64] * 4
     rc = ctypes.c_int(-1)
     lib.launch(ctypes.c_void_p(q), ctypes.c_void_p(k), ctypes.c_void_p(v), ctypes.c_void_p(o), B, H, S,
-               *strides, H if kv_heads is None else kv_heads, ctypes.c_void_p(lse), ctypes.c_bool(False),
+               *strides, H if kv_heads is None else kv_heads, S if Sk is None else Sk, ctypes.c_void_p(lse), ctypes.c_bool(False),
                ctypes.c_float(0.125), ctypes.c_void_p(0), ctypes.byref(rc))
     return rc.value
 
@@ -57,4 +57,5 @@ def test_launch_rejects_bad_arguments_without_touching_the_gpu(built_kernels):
     assert _call(lib, S=256, B=2, strides=[0, 8192, 64] + [8192, 8192, 64] * 3) == 3
     assert _call(lib, H=6, kv_heads=4) == 1     # K/V heads must divide the query heads
     assert _call(lib, H=6, kv_heads=0) == 1
+    assert _call(lib, Sk=0) == 1                # no keys
     assert _call(lib, lse=0x1002) == 2          # fp32 output not 4-byte aligned

@@ -191,7 +191,7 @@ def test_direct_c_abi_call(built_kernels):
         out = torch.zeros_like(q)
         st = [2 * 256 * D, 256 * D, D] * 4
         rc = ctypes.c_int(-1)
-        lib.launch(*(ctypes.c_void_p(t.data_ptr()) for t in (q, k, v, out)), 1, 2, 256, *st, 2, ctypes.c_void_p(0),
+        lib.launch(*(ctypes.c_void_p(t.data_ptr()) for t in (q, k, v, out)), 1, 2, 256, *st, 2, 256, ctypes.c_void_p(0),
                    ctypes.c_bool(True), ctypes.c_float(1.0 / math.sqrt(D)),
                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ctypes.byref(rc))
         assert rc.value == 0
@@ -416,3 +416,31 @@ def test_bf16_operands(S, D, kv_heads, causal):
     assert (out.cpu().float() - want16.float()).abs().max().item() <= BF16_MAX_ABS
     assert ref.calc_diff(out.cpu(), want32) <= BF16_MAX_DIFF
     assert (lse.cpu() - ref.lse_fp32(q.cpu(), ke, causal)).abs().max().item() <= 2e-4
+
+
+# ---------------------------------------------------------------- different numbers of queries and keys
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("Sq,Sk", [(1, 700), (128, 1024), (300, 77), (513, 200), (64, 4096)])
+def test_query_and_key_lengths_differ(variant, Sq, Sk, causal):
+    from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
+    _skip_without_extras(variant)
+    g = torch.Generator().manual_seed(61)
+    B, H, Hkv, D = 2, 4, 2, 128
+    q = torch.randn(B, H, Sq, D, generator=g).half().cuda()
+    k, v = (torch.randn(B, Hkv, Sk, D, generator=g).half().cuda() for _ in range(2))
+    out = torch.zeros_like(q)
+    lse = torch.zeros(B, H, Sq, device="cuda")
+    flash_attn_cute(q, k, v, out, causal=causal, lse=lse)
+    torch.cuda.synchronize()
+    assert flash_attn_status()[0] == 0
+    ke, ve = ref.expand_kv_heads(k.cpu(), v.cpu(), H)
+    qf, kf, vf = q.cpu().float(), ke.float(), ve.float()
+    s = qf @ kf.transpose(-1, -2) / math.sqrt(D)
+    if causal:  # torch's is_causal for a non-square score matrix: aligned to the top left corner
+        s = s.masked_fill(~torch.ones(Sq, Sk, dtype=torch.bool).tril(), float("-inf"))
+    want = torch.softmax(s, -1) @ vf
+    want16 = torch.nn.functional.scaled_dot_product_attention(q.cpu(), ke, ve, is_causal=causal)
+    assert (out.cpu().float() - want16.float()).abs().max().item() <= MAX_ABS
+    assert ref.calc_diff(out.cpu(), want) <= MAX_DIFF
+    tol = 3e-3 if "POLY=16" in variant.split(",") else 2e-4   # see test_lse_output
+    assert (lse.cpu() - torch.logsumexp(s, -1)).abs().max().item() <= tol
