@@ -63,6 +63,7 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   const int bh = blockIdx.y;
   const int b = bh / num_heads;
   const int h = bh - b * num_heads;
+  const int h_kv = h / kv_group;  // K/V head of this query head (one division per CTA, not per copy)
 
   if (tid == 0) {
     *abort_flag = (*reinterpret_cast<volatile int*>(&fray_attn_status[0]) != 0) ? 2u : 0u;
@@ -118,11 +119,11 @@ attn_fwd_simple_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_expect_tx(bar_k, Cfg::kKVBytes);
 #pragma unroll
       for (int p = 0; p < Cfg::kHalves; ++p)
-        tma_load_4d(k_smem + p * Cfg::kKVPanelBytes, &tm_k, bar_k, p * 64, j * BN, h / kv_group, b);
+        tma_load_4d(k_smem + p * Cfg::kKVPanelBytes, &tm_k, bar_k, p * 64, j * BN, h_kv, b);
       mbar_expect_tx(bar_v, Cfg::kKVBytes);
 #pragma unroll
       for (int p = 0; p < Cfg::kHalves; ++p)
-        tma_load_4d(v_smem + p * Cfg::kKVPanelBytes, &tm_v, bar_v, p * 64, j * BN, h / kv_group, b);
+        tma_load_4d(v_smem + p * Cfg::kKVPanelBytes, &tm_v, bar_v, p * 64, j * BN, h_kv, b);
       if (j == 0) mbar_wait(bar_q, 0, abort_flag, 0x101);
       mbar_wait(bar_k, ph, abort_flag, 0x102, j);
       tc_fence_after_sync();

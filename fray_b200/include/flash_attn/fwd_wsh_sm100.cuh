@@ -130,6 +130,7 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int bh = blockIdx.y;
   const int b = bh / num_heads;
   const int h_idx = bh - b * num_heads;
+  const int h_kv = h_idx / kv_group;  // K/V head of this query head (one division per CTA, not per copy)
 
   // Number of 128-key K/V tiles each query tile consumes (0 = tile lies past the end of the sequence).
   const int n_kv = (seq_k + BN - 1) / BN;  // seq_len counts queries, seq_k keys
@@ -167,9 +168,29 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(kv_empty + s, 1);
     }
     fence_barrier_init();
-    prefetch_tensormap(&tm_q);
-    prefetch_tensormap(&tm_k);
-    prefetch_tensormap(&tm_v);
+    // The first copies (Q of both tiles, K_0, V_0) go out right here, before tensor memory is
+    // allocated and the roles separate, so that their latency overlaps the rest of the set-up.  The
+    // producer warp continues with the third ring entry.
+    if (kEarlyCopies && *abort_flag == 0 && n_max > 0) {
+      auto early_q = [&](int i) {
+        if ((i ? n_t1 : n_t0) > 0) {
+          mbar_expect_tx(q_full + i, Cfg::kQTileBytes);
+          for (int p = 0; p < Cfg::kPanels; ++p)
+            tma_load_4d(q_smem + i * Cfg::kQTileBytes + p * Cfg::kQPanelBytes, &tm_q, q_full + i, p * 64,
+                        m0 + i * Cfg::BM, h_idx, b);
+        }
+      };
+      auto early_kv = [&](int t) {
+        mbar_expect_tx(kv_full + t, Cfg::kKVTileBytes);
+        for (int p = 0; p < Cfg::kPanels; ++p)
+          tma_load_4d(kv_smem + t * Cfg::kKVTileBytes + p * Cfg::kKVPanelBytes, t ? &tm_v : &tm_k, kv_full + t, p * 64,
+                      0, h_kv, b);
+      };
+      early_q(0);
+      early_kv(0);
+      early_q(1);
+      early_kv(1);
+    }
     prefetch_tensormap(&tm_o);
   }
   __syncthreads();
@@ -267,11 +288,6 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mbar_wait(l_ready + i, 0, abort_flag, 0x721 + i, h_i);
         const float l = l_buf[i * 128 + r];
         const float inv_l = l > 0.f ? 1.f / l : 1.f;
-        if (lse != nullptr && m0 + i * Cfg::BM + r < seq_len) {
-          const float m = m_buf[i * 128 + r];
-          lse[(static_cast<size_t>(b) * num_heads + h_idx) * seq_len + m0 + i * Cfg::BM + r] =
-              l > 0.f ? (m * scale_log2 + log2f(l)) * 0.69314718055994531f : -INFINITY;
-        }
         mbar_wait(o_final + i, 0, abort_flag, 0x731 + i, h_i);
         tc_fence_after_sync();
         if (r == 0) FRAY_TRACE(6, 1, i);
@@ -302,18 +318,25 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tma_store_4d(&tm_o, o_tile + p * Cfg::kQPanelBytes, p * 64, m0 + i * Cfg::BM, h_idx, b);
           tma_store_commit();
         }
+        if (lse != nullptr && m0 + i * Cfg::BM + r < seq_len) {
+          // log-sum-exp in natural units, written after the tile is on its way: nothing waits for this
+          const float m = m_buf[i * 128 + r];
+          lse[(static_cast<size_t>(b) * num_heads + h_idx) * seq_len + m0 + i * Cfg::BM + r] =
+              l > 0.f ? (m * scale_log2 + log2f(l)) * 0.69314718055994531f : -INFINITY;
+        }
       }
     }
     if (r == 0) {
       FRAY_TRACE(6, 1, 2);
-      tma_store_wait_all();
+      tma_store_wait_read();  // shared memory may go once the copies have read it; the writes finish on their own
       FRAY_TRACE(6, 1, 3);
     }
   } else {
     set_max_regs_dec<Cfg::kRegsOther>();
     if (warp == 13 && lane == 0) {
       // ============================================================= TMA producer
-      auto load_q = [&](int i) __attribute__((always_inline)) {
+      // ring entries 0 and 1 and both Q tiles were issued during set-up (unless that is switched off)
+      auto late_q = [&](int i) __attribute__((always_inline)) {
         if ((i ? n_t1 : n_t0) > 0) {
           mbar_expect_tx(q_full + i, Cfg::kQTileBytes);
 #pragma unroll
@@ -322,8 +345,10 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                         m0 + i * Cfg::BM, h_idx, b);
         }
       };
-      load_q(0);
-      for (int t = 0; t < 2 * n_max; ++t) {
+      if (!kEarlyCopies) {
+        late_q(0);
+      }
+      for (int t = kEarlyCopies ? 2 : 0; t < 2 * n_max; ++t) {
         const int slot = t % STAGES;
         const uint32_t ph = (t / STAGES) & 1;
         mbar_wait(kv_empty + slot, ph ^ 1, abort_flag, 0x401, t);
@@ -333,8 +358,8 @@ attn_fwd_wsh_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int p = 0; p < Cfg::kPanels; ++p)
           tma_load_4d(kv_smem + slot * Cfg::kKVTileBytes + p * Cfg::kKVPanelBytes, tm, kv_full + slot, p * 64,
-                      (t >> 1) * BN, h_idx / kv_group, b);
-        if (t == 0) load_q(1);
+                      (t >> 1) * BN, h_kv, b);
+        if (!kEarlyCopies && t == 0) late_q(1);
       }
     } else if (warp == 12) {
       // ============================================================= MMA issue (whole warp, one elected lane issues)

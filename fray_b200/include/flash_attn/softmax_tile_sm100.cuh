@@ -46,6 +46,14 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 #endif
 static constexpr bool kSfuTurns = FRAY_SFU_TURNS != 0;
 
+// Whether the first copies of a CTA are issued during set-up, before the roles separate
+// (-DFRAY_EARLY_COPIES=0/1).  Measured on one box: +3 % for the whole-tile kernel on short causal
+// CTAs, nothing on the headline shape, -4 % for the half-step kernel; off.
+#ifndef FRAY_EARLY_COPIES
+#define FRAY_EARLY_COPIES 0
+#endif
+static constexpr bool kEarlyCopies = FRAY_EARLY_COPIES != 0;
+
 // Timeline stamps inside the softmax step (compiled in with -DFRAY_ATTN_TRACE only): `tr` points at
 // this step's slot of event 0 in the caller's table, or is null; event e lives e*80 words further.
 #ifdef FRAY_ATTN_TRACE
