@@ -163,6 +163,49 @@ inline int read_attn_trace(unsigned int* out, int max_words) {
 #endif
 
 
+// Epilogue of one query tile, run by the 128 threads that own its rows (thread r = row r, reading its
+// own tensor-memory lane): O / l -> 16-bit -> shared memory (the tile's dead Q buffer, 128B-swizzled)
+// -> TMA store, and the row's log-sum-exp when asked for.  t_o includes the thread's lane offset; m is
+// the row's final exponent offset in score units; barrier_id names a 128-thread barrier of the group.
+// The thread with r == 0 issues and commits the store; it must wait for the store's reads of shared
+// memory (tma_store_wait_read) before the CTA ends.
+template <class Cfg, int D>
+__device__ __forceinline__ void epilogue_tile(uint32_t t_o, uint8_t* o_tile, int r, float l, float m,
+                                              const CUtensorMap* tm_o, int row0, int h, int b, int num_heads,
+                                              int seq_len, float scale_log2, float* lse, int barrier_id) {
+  const float inv_l = l > 0.f ? 1.f / l : 1.f;
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) {
+    uint32_t orr[32];
+    tmem_ld_x32(t_o + c * 32, orr);
+    tmem_wait_ld();
+    uint8_t* panel_row = o_tile + (c >> 1) * Cfg::kQPanelBytes + r * 128;
+#pragma unroll
+    for (int x = 0; x < 32; x += 8) {
+      uint4 v4;
+      v4.x = pack_half2(__uint_as_float(orr[x + 0]) * inv_l, __uint_as_float(orr[x + 1]) * inv_l);
+      v4.y = pack_half2(__uint_as_float(orr[x + 2]) * inv_l, __uint_as_float(orr[x + 3]) * inv_l);
+      v4.z = pack_half2(__uint_as_float(orr[x + 4]) * inv_l, __uint_as_float(orr[x + 5]) * inv_l);
+      v4.w = pack_half2(__uint_as_float(orr[x + 6]) * inv_l, __uint_as_float(orr[x + 7]) * inv_l);
+      const int chunk = (c & 1) * 4 + (x >> 3);  // 16-byte chunk inside the 128-byte row
+      *reinterpret_cast<uint4*>(panel_row + ((chunk ^ (r & 7)) << 4)) = v4;
+    }
+  }
+  fence_proxy_async_smem();
+  named_barrier_sync(barrier_id, 128);
+  if (r == 0) {
+#pragma unroll
+    for (int p = 0; p < Cfg::kPanels; ++p) tma_store_4d(tm_o, o_tile + p * Cfg::kQPanelBytes, p * 64, row0, h, b);
+    tma_store_commit();
+  }
+  if (lse != nullptr && row0 + r < seq_len) {
+    // log-sum-exp of the scaled scores in natural units: offset plus log of the row sum (written
+    // after the tile is on its way: nothing waits for this)
+    lse[(static_cast<size_t>(b) * num_heads + h) * seq_len + row0 + r] =
+        l > 0.f ? (m * scale_log2 + log2f(l)) * 0.69314718055994531f : -INFINITY;
+  }
+}
+
 template <int D, int BN, int STAGES, int POLY, int SPLIT, int KA>
 __global__ void __launch_bounds__(SPLIT == 2 ? 768 : 512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -312,10 +355,18 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
       }
       if (n_i > 0) {
-        l_buf[i * 128 + r] = l_run;
-        m_buf[i * 128 + r] = m_ref;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(corr_ready + i);
+        // The group writes its own tile out: it has the row sums and offsets in registers, its threads
+        // sit on the rows' tensor-memory lanes, and the two tiles' epilogues then run side by side
+        // instead of one after the other in the correction group.
+        mbar_wait(o_full + i, (n_i - 1) & 1, abort_flag, 0x331 + i, n_i);
+        tc_fence_after_sync();
+        if (r == 0) FRAY_TRACE(6, 1, i);  // last P.V of tile i complete, epilogue starts
+        epilogue_tile<Cfg, D>(tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1) + lane_base, q_smem + i * Cfg::kQTileBytes,
+                              r, l_run, m_ref, &tm_o, m0 + i * Cfg::BM, h, b, num_heads, seq_len, scale_log2, lse, 4 + i);
+        if (r == 0) {
+          tma_store_wait_read();  // shared memory may go once the copy has read it; the writes finish on their own
+          FRAY_TRACE(6, 1, 2 + i);
+        }
       }
     } else if constexpr (SPLIT == 3) {
       // Keys [0,KA) of every step; the helper group takes the rest and owns the O rescaling.
@@ -473,60 +524,31 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         }
       }
     }
-    // Epilogue: O_i / l_i -> fp16 -> shared memory (the dead Q_i buffer, 128B-swizzled) -> TMA store.
+    // Epilogue (variants with several softmax threads per row; with one thread per row the softmax
+    // groups write their own tiles): row sums and offsets come through shared memory.
+    if constexpr (SPLIT != 1) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int n_i = i ? n_t1 : n_t0;
-      if (n_i > 0) {
-        const uint32_t ph = (n_i - 1) & 1;
-        // corr_ready completes once per published alpha and once for the final row sum; in the helper
-        // variant only the latter happens
-        mbar_wait(corr_ready + i, Cfg::kHelper ? 0u : ph, abort_flag, 0x321 + i, n_i);
-        const float l = l_buf[i * 128 + r] + (Cfg::kHelper ? (i ? l_help1 : l_help0) : 0.f);
-        const float inv_l = l > 0.f ? 1.f / l : 1.f;
-        mbar_wait(o_full + i, ph, abort_flag, 0x331 + i, n_i);
-        tc_fence_after_sync();
-        if (r == 0) FRAY_TRACE(6, 1, i);  // last P.V of tile i complete, epilogue starts
-        const uint32_t t_o = tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1) + lane_base;
-        uint8_t* o_tile = q_smem + i * Cfg::kQTileBytes;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t orr[32];
-          tmem_ld_x32(t_o + c * 32, orr);
-          tmem_wait_ld();
-          uint8_t* panel_row = o_tile + (c >> 1) * Cfg::kQPanelBytes + r * 128;
-#pragma unroll
-          for (int x = 0; x < 32; x += 8) {
-            uint4 v4;
-            v4.x = pack_half2(__uint_as_float(orr[x + 0]) * inv_l, __uint_as_float(orr[x + 1]) * inv_l);
-            v4.y = pack_half2(__uint_as_float(orr[x + 2]) * inv_l, __uint_as_float(orr[x + 3]) * inv_l);
-            v4.z = pack_half2(__uint_as_float(orr[x + 4]) * inv_l, __uint_as_float(orr[x + 5]) * inv_l);
-            v4.w = pack_half2(__uint_as_float(orr[x + 6]) * inv_l, __uint_as_float(orr[x + 7]) * inv_l);
-            const int chunk = (c & 1) * 4 + (x >> 3);  // 16-byte chunk inside the 128-byte row
-            *reinterpret_cast<uint4*>(panel_row + ((chunk ^ (r & 7)) << 4)) = v4;
-          }
-        }
-        fence_proxy_async_smem();
-        named_barrier_sync(1, 128);
-        if (r == 0) {
-#pragma unroll
-          for (int p = 0; p < Cfg::kPanels; ++p)
-            tma_store_4d(&tm_o, o_tile + p * Cfg::kQPanelBytes, p * 64, m0 + i * Cfg::BM, h, b);
-          tma_store_commit();
-        }
-        if (lse != nullptr && m0 + i * Cfg::BM + r < seq_len) {
-          // log-sum-exp of the scaled scores in natural units: offset plus log of the row sum
-          // (after the tile is on its way: nothing waits for this)
-          const float m = m_buf[i * 128 + r];
-          lse[(static_cast<size_t>(b) * num_heads + h) * seq_len + m0 + i * Cfg::BM + r] =
-              l > 0.f ? (m * scale_log2 + log2f(l)) * 0.69314718055994531f : -INFINITY;
+      for (int i = 0; i < 2; ++i) {
+        const int n_i = i ? n_t1 : n_t0;
+        if (n_i > 0) {
+          const uint32_t ph = (n_i - 1) & 1;
+          // corr_ready completes once per published alpha and once for the final row sum; in the helper
+          // variant only the latter happens
+          mbar_wait(corr_ready + i, Cfg::kHelper ? 0u : ph, abort_flag, 0x321 + i, n_i);
+          const float l = l_buf[i * 128 + r] + (Cfg::kHelper ? (i ? l_help1 : l_help0) : 0.f);
+          mbar_wait(o_full + i, ph, abort_flag, 0x331 + i, n_i);
+          tc_fence_after_sync();
+          if (r == 0) FRAY_TRACE(6, 1, i);  // last P.V of tile i complete, epilogue starts
+          epilogue_tile<Cfg, D>(tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1) + lane_base,
+                                q_smem + i * Cfg::kQTileBytes, r, l, m_buf[i * 128 + r], &tm_o, m0 + i * Cfg::BM, h, b,
+                                num_heads, seq_len, scale_log2, lse, 1);
         }
       }
-    }
-    if (r == 0) {
-      FRAY_TRACE(6, 1, 2);  // stores issued
-      tma_store_wait_read();  // shared memory may go once the copies have read it; the writes finish on their own
-      FRAY_TRACE(6, 1, 3);  // stores complete
+      if (r == 0) {
+        FRAY_TRACE(6, 1, 2);  // stores issued
+        tma_store_wait_read();  // shared memory may go once the copies have read it; the writes finish on their own
+        FRAY_TRACE(6, 1, 3);
+      }
     }
   } else {
     set_max_regs_dec<Cfg::kRegsOther>();
