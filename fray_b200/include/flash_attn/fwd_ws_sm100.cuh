@@ -648,9 +648,11 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         FRAY_TRACE(7, i, j);
       };
 
-#if FRAY_COMPACT_MMA_ROLE
+      if constexpr (FRAY_COMPACT_MMA_ROLE != 0 && SPLIT == 1) {
       // One copy of each issue sequence, the tile index a run-time value: the kernels are sensitive
       // to instruction fetch, and this role's code is otherwise there once per tile and call site.
+      // (One thread per row only: the 768-thread split-row variant, whose MMA warp has 56 registers,
+      // stopped making progress with it - bounded waits, status 0x302 - and was left as it was.)
 #pragma unroll 1
       for (int i = 0; i < 2; ++i) {
         if ((i ? n1 : n0) > 0) {
@@ -668,7 +670,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
         }
       }
-#else
+      } else {
       if (n0 > 0) {
         mbar_wait(q_full + 0, 0, abort_flag, 0x511);
         issue_qk(0, 0);
@@ -687,7 +689,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           if (j + 1 < n1) issue_qk(1, j + 1);
         }
       }
-#endif
+      }
     }
   }
 
