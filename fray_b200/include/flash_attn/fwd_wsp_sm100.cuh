@@ -121,96 +121,117 @@ struct WspMmaCtx {
 };
 
 // S_i = Q_i . K^T with K in ring entry t.  new_q: first use of a freshly loaded Q tile; last_user
-// releases the ring entry, last_qk the Q buffer.
-template <class Cfg, int D, int BN, int STAGES, int I>
-__device__ __forceinline__ void wsp_issue_qk(const WspMmaCtx& c, uint32_t t, bool new_q, bool last_user, bool last_qk,
-                                             uint32_t& q_count) {
+// releases the ring entry, last_qk the Q buffer.  The tile index i is a run-time value: one copy of
+// the sequence serves both tiles and every call site (the kernel is instruction-fetch sensitive).
+template <class Cfg, int D, int BN, int STAGES>
+__device__ __forceinline__ void wsp_issue_qk(const WspMmaCtx& c, int i, uint32_t t, bool new_q, bool last_user,
+                                             bool last_qk, uint32_t& q_count) {
   constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);
   constexpr uint32_t kIdescQK = idesc_f16_f32(Cfg::BM, BN, false, false);
+  constexpr uint32_t kDescHi = static_cast<uint32_t>(kDescK >> 32);
+  constexpr uint32_t kDescLo = static_cast<uint32_t>(kDescK);
   const int slot = t % STAGES;
   mbar_wait(c.kv_full + slot, (t / STAGES) & 1, c.abort_flag, 0x901, t);
   if (new_q) {
-    mbar_wait(c.q_full + I, q_count & 1, c.abort_flag, 0x911 + I, t);
+    mbar_wait(c.q_full + i, q_count & 1, c.abort_flag, 0x911 + i, t);
     ++q_count;
   }
   tc_fence_after_sync();
-  const uint64_t qd = smem_desc_at(kDescK, c.q_addr + I * Cfg::kQTileBytes);
-  const uint64_t kd = smem_desc_at(kDescK, c.kv_addr + slot * Cfg::kKVTileBytes);
-  const uint32_t t_s = c.tmem_base + (I == 0 ? Cfg::kColS0 : Cfg::kColS1);
+  const uint32_t q_lo = kDescLo | (((c.q_addr + i * Cfg::kQTileBytes) & 0x3FFFF) >> 4);
+  const uint32_t k_lo = kDescLo | (((c.kv_addr + slot * Cfg::kKVTileBytes) & 0x3FFFF) >> 4);
+  const uint32_t t_s = c.tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
     const uint32_t koff = ((kk >> 2) * Cfg::kKVPanelBytes + (kk & 3) * 32) >> 4;
-    mma_ss_elect(t_s, qd + qoff, kd + koff, kIdescQK, kk > 0);
+    mma_ss_elect_lohi(t_s, q_lo + qoff, kDescHi, k_lo + koff, kDescHi, kIdescQK, kk > 0);
   }
-  mma_commit_elect(c.s_full + I);
+  mma_commit_elect(c.s_full + i);
   if (last_user) mma_commit_elect(c.kv_empty + slot);
-  if (last_qk) mma_commit_elect(c.q_empty + I);
+  if (last_qk) mma_commit_elect(c.q_empty + i);
 }
 
 // O_i (+)= P_i . V with V in ring entry t, chunk by chunk as P arrives.
-template <class Cfg, int D, int BN, int STAGES, int I>
-__device__ __forceinline__ void wsp_issue_pv(const WspMmaCtx& c, int j, uint32_t t, bool last_user, uint32_t& pv_count,
-                                             uint32_t& resc_count, uint32_t items_done) {
+template <class Cfg, int D, int BN, int STAGES>
+__device__ __forceinline__ void wsp_issue_pv(const WspMmaCtx& c, int i, int j, uint32_t t, bool last_user,
+                                             uint32_t& pv_count, uint32_t& resc_count, uint32_t items_done) {
   constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kKVPanelBytes, 1024);
   constexpr uint32_t kIdescPV = idesc_f16_f32(Cfg::BM, D, false, true);
+  constexpr uint32_t kDescVHi = static_cast<uint32_t>(kDescV >> 32);
   constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
   const int slot = t % STAGES;
   mbar_wait(c.kv_full + slot, (t / STAGES) & 1, c.abort_flag, 0x902, t);
   if (j > 0) {
-    mbar_wait(c.o_rescaled + I, resc_count & 1, c.abort_flag, 0x905 + I, j);
+    mbar_wait(c.o_rescaled + i, resc_count & 1, c.abort_flag, 0x905 + i, j);
     ++resc_count;
   } else if (items_done > 0) {
-    mbar_wait(c.o_free + I, (items_done - 1) & 1, c.abort_flag, 0x907 + I, j);
+    mbar_wait(c.o_free + i, (items_done - 1) & 1, c.abort_flag, 0x907 + i, j);
   }
-  const uint64_t vd = smem_desc_at(kDescV, c.kv_addr + slot * Cfg::kKVTileBytes);
-  const uint32_t t_p = c.tmem_base + (I == 0 ? Cfg::kColS0 : Cfg::kColS1);
-  const uint32_t t_o = c.tmem_base + (I == 0 ? Cfg::kColO0 : Cfg::kColO1);
+  const uint32_t v_lo = static_cast<uint32_t>(kDescV) | (((c.kv_addr + slot * Cfg::kKVTileBytes) & 0x3FFFF) >> 4);
+  const uint32_t t_p = c.tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
+  const uint32_t t_o = c.tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
 #pragma unroll
   for (int q = 0; q < Cfg::kPChunks; ++q) {
-    FRAY_CRIT_WAIT(c.p_full + I * Cfg::kPChunks + q, pv_count & 1, c.abort_flag, 0x903 + I, j);
+    FRAY_CRIT_WAIT(c.p_full + i * Cfg::kPChunks + q, pv_count & 1, c.abort_flag, 0x903 + i, j);
     tc_fence_after_sync();
 #pragma unroll
     for (int s2 = 0; s2 < kStepsPerChunk; ++s2) {
       const int kk = q * kStepsPerChunk + s2;
-      mma_ts_elect(t_o, t_p + kk * 8, vd + ((kk * 2048) >> 4), kIdescPV, (j > 0 || kk > 0));
+      mma_ts_elect_lohi(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
     }
   }
   ++pv_count;
-  mma_commit_elect(c.o_full + I);
+  mma_commit_elect(c.o_full + i);
   if (last_user) mma_commit_elect(c.kv_empty + slot);
 }
 
 // One tile's share of KV step j of item w (j = -1: the item's lead-in, where only a first Q.K^T may
-// be due).  nx is the next item of this CTA (valid when has_next).
-template <class Cfg, int D, int BN, int STAGES, int I>
-__device__ __forceinline__ void wsp_tile_step(const WspMmaCtx& c, const WspItem& w, const WspItem& nx, bool has_next,
-                                              int j, uint32_t t_base, uint32_t t_next, uint32_t& q_count,
-                                              uint32_t& pv_count, uint32_t& resc_count, uint32_t& items_done,
-                                              bool& started) {
-  const int n_i = I ? w.n1 : w.n0;
+// be due).  nx is the next item of this CTA (valid when has_next).  At most one P.V and one Q.K^T are
+// issued; which Q.K^T (the next step's, the item's first, or the next item's first) is decided first
+// so that the sequence itself exists once.
+template <class Cfg, int D, int BN, int STAGES>
+__device__ __forceinline__ void wsp_tile_step(const WspMmaCtx& c, int i, const WspItem& w, const WspItem& nx,
+                                              bool has_next, int j, uint32_t t_base, uint32_t t_next,
+                                              uint32_t& q_count, uint32_t& pv_count, uint32_t& resc_count,
+                                              uint32_t& items_done, bool& started) {
+  const int n_i = i ? w.n1 : w.n0;
   if (n_i == 0) return;
   if (j >= 0 && j < n_i)
-    wsp_issue_pv<Cfg, D, BN, STAGES, I>(c, j, t_base + 2 * j + 1, (I == 1) || !(j < w.n1), pv_count, resc_count,
-                                        items_done);
+    wsp_issue_pv<Cfg, D, BN, STAGES>(c, i, j, t_base + 2 * j + 1, (i == 1) || !(j < w.n1), pv_count, resc_count,
+                                     items_done);
+  bool do_qk = false, new_q = false, last_user = false, last_qk = false;
+  uint32_t t_qk = 0;
   if (j + 1 < n_i) {
     if (j >= 0) {
-      wsp_issue_qk<Cfg, D, BN, STAGES, I>(c, t_base + 2 * (j + 1), false, (I == 1) || !(j + 1 < w.n1), j + 2 == n_i,
-                                          q_count);
+      do_qk = true;
+      t_qk = t_base + 2 * (j + 1);
+      last_user = (i == 1) || !(j + 1 < w.n1);
+      last_qk = j + 2 == n_i;
     } else {
-      if (!started) wsp_issue_qk<Cfg, D, BN, STAGES, I>(c, t_base, true, (I == 1) || !(0 < w.n1), n_i == 1, q_count);
+      if (!started) {
+        do_qk = true;
+        t_qk = t_base;
+        new_q = true;
+        last_user = (i == 1) || !(0 < w.n1);
+        last_qk = n_i == 1;
+      }
       started = false;
     }
   } else if (j + 1 == n_i) {
-    // Tile I has finished this item.  Start it on the next item right away when the ring can hold
+    // Tile i has finished this item.  Start it on the next item right away when the ring can hold
     // that item's K_0 beside everything the other tile still needs.
     ++items_done;
-    const int nn_i = I ? nx.n1 : nx.n0;
+    const int nn_i = i ? nx.n1 : nx.n0;
     if (has_next && nn_i > 0 && 2 * (w.n_max - n_i) + 2 <= STAGES) {
-      wsp_issue_qk<Cfg, D, BN, STAGES, I>(c, t_next, true, (I == 1) || !(0 < nx.n1), nn_i == 1, q_count);
+      do_qk = true;
+      t_qk = t_next;
+      new_q = true;
+      last_user = (i == 1) || !(0 < nx.n1);
+      last_qk = nn_i == 1;
       started = true;
     }
   }
+  if (do_qk) wsp_issue_qk<Cfg, D, BN, STAGES>(c, i, t_qk, new_q, last_user, last_qk, q_count);
 }
 
 template <int D, int BN, int STAGES, int POLY>
@@ -480,10 +501,21 @@ attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         if (has_next) nx = wsp_decode_item<Cfg::BM, BN>(item + item_step, n_pairs, num_heads, seq_len, causal);
         const uint32_t t_next = t_base + 2 * w.n_max;  // ring index of the next item's K_0
         for (int j = -1; j < w.n_max; ++j) {
-          wsp_tile_step<Cfg, D, BN, STAGES, 0>(ctx, w, nx, has_next, j, t_base, t_next, q_count0, pv_count0, resc_count0,
-                                               items_done0, started0);
-          wsp_tile_step<Cfg, D, BN, STAGES, 1>(ctx, w, nx, has_next, j, t_base, t_next, q_count1, pv_count1, resc_count1,
-                                               items_done1, started1);
+#pragma unroll 1
+          for (int i = 0; i < 2; ++i) {
+            // per-tile progress lives in scalars; pick this tile's, run the step, put them back
+            uint32_t qc = i ? q_count1 : q_count0, pc = i ? pv_count1 : pv_count0, rc = i ? resc_count1 : resc_count0;
+            uint32_t dn = i ? items_done1 : items_done0;
+            bool st = i ? started1 : started0;
+            if (j >= 0) FRAY_TRACE(1, i, pc);  // MMA warp reaches tile i's share of step j
+            wsp_tile_step<Cfg, D, BN, STAGES>(ctx, i, w, nx, has_next, j, t_base, t_next, qc, pc, rc, dn, st);
+            if (j >= 0) FRAY_TRACE(2, i, pc - 1);  // ... and leaves it
+            if (i) {
+              q_count1 = qc, pv_count1 = pc, resc_count1 = rc, items_done1 = dn, started1 = st;
+            } else {
+              q_count0 = qc, pv_count0 = pc, resc_count0 = rc, items_done0 = dn, started0 = st;
+            }
+          }
         }
         t_base = t_next;
       }
