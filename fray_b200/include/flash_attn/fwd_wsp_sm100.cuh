@@ -118,7 +118,19 @@ struct WspMmaCtx {
   uint64_t* p_full;
   volatile uint32_t* abort_flag;
   uint32_t q_addr, kv_addr, tmem_base;
+#ifdef FRAY_ATTN_TRACE
+  unsigned int* trace_sm;  // timeline table of the traced CTA, null elsewhere
+#endif
 };
+#ifdef FRAY_ATTN_TRACE
+#define WSP_TRACE(c, event, tile, iter)                                                                   \
+  do {                                                                                                    \
+    if ((c).trace_sm != nullptr && (iter) < kTraceIters)                                                  \
+      (c).trace_sm[((event) * 2 + (tile)) * kTraceIters + (iter)] = static_cast<unsigned int>(clock64()); \
+  } while (0)
+#else
+#define WSP_TRACE(c, event, tile, iter) do { } while (0)
+#endif
 
 // S_i = Q_i . K^T with K in ring entry t.  new_q: first use of a freshly loaded Q tile; last_user
 // releases the ring entry, last_qk the Q buffer.  The tile index i is a run-time value: one copy of
@@ -137,6 +149,7 @@ __device__ __forceinline__ void wsp_issue_qk(const WspMmaCtx& c, int i, uint32_t
     ++q_count;
   }
   tc_fence_after_sync();
+  WSP_TRACE(c, 5, i, t >> 1);  // K tile (and Q) present
   const uint32_t q_lo = kDescLo | (((c.q_addr + i * Cfg::kQTileBytes) & 0x3FFFF) >> 4);
   const uint32_t k_lo = kDescLo | (((c.kv_addr + slot * Cfg::kKVTileBytes) & 0x3FFFF) >> 4);
   const uint32_t t_s = c.tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
@@ -149,6 +162,7 @@ __device__ __forceinline__ void wsp_issue_qk(const WspMmaCtx& c, int i, uint32_t
   mma_commit_elect(c.s_full + i);
   if (last_user) mma_commit_elect(c.kv_empty + slot);
   if (last_qk) mma_commit_elect(c.q_empty + i);
+  WSP_TRACE(c, 7, i, t >> 1);  // S issued
 }
 
 // O_i (+)= P_i . V with V in ring entry t, chunk by chunk as P arrives.
@@ -160,20 +174,31 @@ __device__ __forceinline__ void wsp_issue_pv(const WspMmaCtx& c, int i, int j, u
   constexpr uint32_t kDescVHi = static_cast<uint32_t>(kDescV >> 32);
   constexpr int kStepsPerChunk = (BN / 16) / Cfg::kPChunks;
   const int slot = t % STAGES;
-  mbar_wait(c.kv_full + slot, (t / STAGES) & 1, c.abort_flag, 0x902, t);
-  if (j > 0) {
-    mbar_wait(c.o_rescaled + i, resc_count & 1, c.abort_flag, 0x905 + i, j);
-    ++resc_count;
-  } else if (items_done > 0) {
-    mbar_wait(c.o_free + i, (items_done - 1) & 1, c.abort_flag, 0x907 + i, j);
+  // A wait on an mbarrier costs this warp a shared-memory round trip (50-100 cycles) even when the
+  // phase is long complete.  When this warp arrives late, everything is: test all barriers of the
+  // step together first (the round trips overlap) and fall back to the one-by-one waits otherwise.
+  uint64_t* b_o = j > 0 ? c.o_rescaled + i : c.o_free + i;
+  const uint32_t par_o = j > 0 ? (resc_count & 1) : ((items_done - 1) & 1);
+  const bool need_o = j > 0 || items_done > 0;
+  bool ready = mbar_test_wait(c.kv_full + slot, (t / STAGES) & 1);  // non-blocking tests
+#pragma unroll
+  for (int q = 0; q < Cfg::kPChunks; ++q) ready = ready & mbar_test_wait(c.p_full + i * Cfg::kPChunks + q, pv_count & 1);
+  if (need_o) ready = ready & mbar_test_wait(b_o, par_o);
+  if (!ready) {
+    mbar_wait(c.kv_full + slot, (t / STAGES) & 1, c.abort_flag, 0x902, t);
+    if (need_o) mbar_wait(b_o, par_o, c.abort_flag, (j > 0 ? 0x905 : 0x907) + i, j);
   }
+  if (j > 0) ++resc_count;
   const uint32_t v_lo = static_cast<uint32_t>(kDescV) | (((c.kv_addr + slot * Cfg::kKVTileBytes) & 0x3FFFF) >> 4);
   const uint32_t t_p = c.tmem_base + (i == 0 ? Cfg::kColS0 : Cfg::kColS1);
   const uint32_t t_o = c.tmem_base + (i == 0 ? Cfg::kColO0 : Cfg::kColO1);
+  if (ready) tc_fence_after_sync();
 #pragma unroll
   for (int q = 0; q < Cfg::kPChunks; ++q) {
-    FRAY_CRIT_WAIT(c.p_full + i * Cfg::kPChunks + q, pv_count & 1, c.abort_flag, 0x903 + i, j);
-    tc_fence_after_sync();
+    if (!ready) {
+      FRAY_CRIT_WAIT(c.p_full + i * Cfg::kPChunks + q, pv_count & 1, c.abort_flag, 0x903 + i, j);
+      tc_fence_after_sync();
+    }
 #pragma unroll
     for (int s2 = 0; s2 < kStepsPerChunk; ++s2) {
       const int kk = q * kStepsPerChunk + s2;
@@ -183,6 +208,7 @@ __device__ __forceinline__ void wsp_issue_pv(const WspMmaCtx& c, int i, int j, u
   ++pv_count;
   mma_commit_elect(c.o_full + i);
   if (last_user) mma_commit_elect(c.kv_empty + slot);
+  WSP_TRACE(c, 3, i, pv_count - 1);  // P.V issued
 }
 
 // One tile's share of KV step j of item w (j = -1: the item's lead-in, where only a first Q.K^T may
@@ -486,7 +512,11 @@ attn_fwd_wsp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // V_j: O_i += P_i(j).V_j - and it carries over from one item to the next, so a tile's first
       // Q.K^T of the next item follows its last P.V directly.
       const WspMmaCtx ctx{kv_full, kv_empty, q_full, q_empty, s_full, o_full, o_rescaled, o_free, p_full,
-                          abort_flag, smem_u32(q_smem), smem_u32(kv_smem), tmem_base};
+                          abort_flag, smem_u32(q_smem), smem_u32(kv_smem), tmem_base
+#ifdef FRAY_ATTN_TRACE
+                          , trace_on ? trace_sm : nullptr
+#endif
+      };
       // per-tile progress, plain scalars
       uint32_t q_count0 = 0, q_count1 = 0;        // q_full phases consumed
       uint32_t pv_count0 = 0, pv_count1 = 0;      // P.V steps issued (phase of the p_full chunks)

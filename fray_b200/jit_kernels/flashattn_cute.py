@@ -96,7 +96,7 @@ def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
 
 
 # Built and tested, but not part of the tuning space: the persistent kernel is correct and hands
-# items over without a bubble, yet its steady state measured ~20 % slower than the non-persistent one.
+# items over without a bubble, yet it measures ~10 % slower than the non-persistent one on the headline shape (and much slower on causal shapes).
 # Likewise the mix of polynomial and special-function exponentials (POLY 1..4), also measured slower.
 EXTRA_VARIANTS = (
     {"KIND": 2, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},
