@@ -7,8 +7,8 @@
 #include "fwd_simple_sm100.cuh"
 #include "host_sm100.cuh"
 #include "fwd_ws_sm100.cuh"
-#include "fwd_wsp_sm100.cuh"
 #include "fwd_wsh_sm100.cuh"
+#include "fwd_ws3_sm100.cuh"
 
 namespace fray {
 
@@ -16,10 +16,11 @@ namespace fray {
 enum AttnKernelKind : int {
   kAttnSimple = 0,  // one 128-row tile per CTA, single role, no overlap
   kAttnWarpSpecialized = 1,  // two 128-row tiles per CTA, producer / MMA / softmax / correction roles
-  kAttnPersistent = 2,       // the same roles in one CTA per SM that loops over work items
   kAttnSplitRow = 3,         // the warp-specialised kernel with two softmax threads per query row (24 warps)
   kAttnHelper = 4,           // the warp-specialised kernel whose correction group takes a share of every row
   kAttnHalfStep = 5,         // warp-specialised, softmax steps of 64 keys in two alternating score buffers per tile
+  kAttnThreeBuffers = 6,     // one 128-row tile per CTA, three score buffers, two softmax groups on alternate KV steps
+  kAttnPaired = 7,           // the same on a pair of CTAs (cta_group::2): 256 rows per pair, half of K and V per CTA
 };
 
 // KIND, D, BLOCK_N, STAGES, POLY are compile-time tuning keys (POLY: how many of every four
@@ -61,14 +62,11 @@ inline void flash_attn_sm100(const operand_t* q, const operand_t* k, const opera
                                                                                  scale, stream);
   } else if constexpr (KIND == kAttnHalfStep) {
     rc = sm100::launch_attn_fwd_wsh<D, STAGES>(q, k, v, o, shp, st, ex, causal, scale, stream);
+  } else if constexpr (KIND == kAttnThreeBuffers) {
+    rc = sm100::launch_attn_fwd_ws3<D, STAGES, 1>(q, k, v, o, shp, st, ex, causal, scale, stream);
   } else {
-    static_assert(KIND == kAttnPersistent, "unknown kernel kind");
-    // the persistent variant stays at the reference's feature set
-    if (ex.kv_group != 1 || ex.lse != nullptr || ex.seq_k != seq_len) {
-      rc = kAttnUnsupported;
-      return;
-    }
-    rc = sm100::launch_attn_fwd_wsp<D, BLOCK_N, STAGES, POLY>(q, k, v, o, shp, st, causal, scale, stream);
+    static_assert(KIND == kAttnPaired, "unknown kernel kind");
+    rc = sm100::launch_attn_fwd_ws3<D, STAGES, 2>(q, k, v, o, shp, st, ex, causal, scale, stream);
   }
 }
 

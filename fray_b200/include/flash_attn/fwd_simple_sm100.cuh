@@ -252,14 +252,8 @@ inline int launch_attn_fwd_simple(const operand_t* q, const operand_t* k, const 
   if (rc != kAttnOk) return rc;
 
   auto kernel = attn_fwd_simple_kernel<D, BN>;
-  static bool attr_done = false;  // one process drives one GPU: set once
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return kAttnSmemAttrFailed;
-    }
-    attr_done = true;
-  }
+  rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes);
+  if (rc != kAttnOk) return rc;
   dim3 grid((shp.S + Cfg::BM - 1) / Cfg::BM, shp.B * shp.H);
   kernel<<<grid, 128, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, o, st[3].b, st[3].h, st[3].s, shp.H, shp.S,
                                                  causal ? 1 : 0, scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k);

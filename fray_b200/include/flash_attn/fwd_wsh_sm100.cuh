@@ -496,14 +496,8 @@ inline int launch_attn_fwd_wsh(const operand_t* q, const operand_t* k, const ope
   if (rc != kAttnOk) return rc;
 
   auto kernel = attn_fwd_wsh_kernel<D, STAGES>;
-  static bool attr_done = false;  // one process drives one GPU: set once
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return kAttnSmemAttrFailed;
-    }
-    attr_done = true;
-  }
+  rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes);
+  if (rc != kAttnOk) return rc;
   dim3 grid((shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM), shp.B * shp.H);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,
                                                            scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k);

@@ -137,6 +137,29 @@ inline int cached_attn_tensor_map(CUtensorMap* map, const void* base, const Attn
   return rc;
 }
 
+// Raises a kernel's dynamic shared-memory limit once per device of this process (function
+// attributes are per device; the reference sets the attribute on every launch,
+// fray/include/flash_attn/flashattn_cute.cuh:231).  Tag makes the bookkeeping unique per kernel
+// configuration: kernels of equal signature share a function-pointer type.
+template <class Tag, class Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, int bytes) {
+  constexpr int kMaxDevices = 64;
+  static bool done[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return kAttnSmemAttrFailed;
+  }
+  const bool tracked = dev >= 0 && dev < kMaxDevices;
+  if (tracked && done[dev]) return kAttnOk;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return kAttnSmemAttrFailed;
+  }
+  if (tracked) done[dev] = true;
+  return kAttnOk;
+}
+
 // Synchronising read of the sticky device status words; clears them when asked.
 inline int read_attn_status(int* out4, bool clear) {
   int host[4] = {0, 0, 0, 0};

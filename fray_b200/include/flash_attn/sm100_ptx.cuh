@@ -169,6 +169,63 @@ __device__ __forceinline__ void mbar_wait_spin(uint64_t* bar, uint32_t parity, v
   }
 }
 
+// ---------------------------------------------------------------- CTA pairs (clusters of two)
+// Rank of this CTA inside its cluster (0 for a kernel launched without clusters).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Shared-memory address of the same object in the CTA of rank `cta` of this cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t cta) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+  return r;
+}
+__device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+// All threads of both CTAs meet; memory operations before it are visible cluster-wide after it.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on an mbarrier named by a cluster-wide address (this CTA's or the peer's).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Waits on a barrier of this CTA that threads of the peer CTA arrive on: acquire at cluster scope.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ void mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                                  uint32_t site, uint32_t extra = 0) {
+  if (mbar_try_wait_cluster(bar, parity)) return;
+  const long long t0 = clock64();
+  uint32_t polls = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++polls & 31u) == 0u) {
+      if (*abort_flag) return;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        report_timeout(abort_flag, site, extra);
+        return;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -182,6 +239,21 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       " [%0], [%1, {%3, %4, %5, %6}], [%2];"
       :
       : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
+        "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// The same copy issued by a CTA of a pair: the data lands in this CTA's shared memory, the byte
+// count is signalled on `bar_cluster_addr`, a cluster-wide mbarrier address that may name the
+// peer CTA's barrier (the pair's leader collects the arrivals of both halves of an operand).
+// No multicast: each CTA fetches exactly the half it holds.
+__device__ __forceinline__ void tma_load_4d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
         "r"(c2), "r"(c3)
       : "memory");
 }
@@ -345,6 +417,70 @@ __device__ __forceinline__ void mma_commit_elect(uint64_t* bar) {
       "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
       "}\n" ::"r"(smem_u32(bar))
       : "memory");
+}
+
+// CTA-pair forms (cta_group::2): issued by one thread of the pair's leader (even rank).  The product
+// has M = 256 rows, 128 per CTA; each CTA supplies its own rows of A (shared memory or tensor memory at
+// the same addresses in both CTAs) and one half of B along N; each CTA's tensor memory receives its 128
+// rows of D.
+template <int CTAS>
+__device__ __forceinline__ void mma_ss_elect_g(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (CTAS == 1) {
+    mma_ss_elect_lohi(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p, e;\n"
+        ".reg .b64 da, db;\n"
+        "mov.b64 da, {%1, %2};\n"
+        "mov.b64 db, {%3, %4};\n"
+        "elect.sync _|e, 0xffffffff;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "@e tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n"
+        "}\n"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+template <int CTAS>
+__device__ __forceinline__ void mma_ts_elect_g(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+  if constexpr (CTAS == 1) {
+    mma_ts_elect_lohi(d_tmem, a_tmem, b_lo, b_hi, idesc, accumulate);
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p, e;\n"
+        ".reg .b64 db;\n"
+        "mov.b64 db, {%2, %3};\n"
+        "elect.sync _|e, 0xffffffff;\n"
+        "setp.ne.b32 p, %5, 0;\n"
+        "@e tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %4, p;\n"
+        "}\n"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// Arrives once on `bar` (the barrier at this shared-memory offset in BOTH CTAs of a pair when CTAS == 2)
+// when every MMA issued so far by the elected thread has completed.
+template <int CTAS>
+__device__ __forceinline__ void mma_commit_elect_g(uint64_t* bar) {
+  if constexpr (CTAS == 1) {
+    mma_commit_elect(bar);
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred e;\n"
+        ".reg .b16 m;\n"
+        "mov.b16 m, 3;\n"
+        "elect.sync _|e, 0xffffffff;\n"
+        "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n"
+        "}\n" ::"r"(smem_u32(bar))
+        : "memory");
+  }
 }
 
 __device__ __forceinline__ void mma_commit_elect_a(uint32_t bar_addr) {

@@ -82,31 +82,20 @@ def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
     POLY: exponential mode of kinds 1-4 (flash_attn/flash_attn_sm100.cuh).
     """
     space = [
-        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # warp-specialised, whole 128-key steps
-        {"KIND": 5, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # warp-specialised, 64-key steps in two score buffers (wins on causal shapes)
+        {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # warp-specialised, two tiles per CTA, whole 128-key steps
+        {"KIND": 5, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # ... 64-key steps in two score buffers per tile
+        {"KIND": 6, "BLOCK_N": 128, "STAGES": 5 if d == 128 else 6, "POLY": 0},   # one tile per CTA, three score buffers
         {"KIND": 0, "BLOCK_N": 128, "STAGES": 1, "POLY": 0},
         {"KIND": 0, "BLOCK_N": 64, "STAGES": 1, "POLY": 0},
     ]
+    if d == 128:
+        space.insert(3, {"KIND": 7, "BLOCK_N": 128, "STAGES": 6, "POLY": 0})  # three score buffers on a CTA pair (cta_group::2)
     forced = os.getenv("FRAY_ATTN_FORCE")  # e.g. "KIND=0,BLOCK_N=64,STAGES=1"
     if forced:
         point = {"POLY": 0}
         point.update({kv.split("=")[0].strip(): int(kv.split("=")[1]) for kv in forced.split(",")})
         return (point,)
     return tuple(space)
-
-
-# Built and tested, but not part of the tuning space: the persistent kernel is correct and hands
-# items over without a bubble, yet it measures ~10 % slower than the non-persistent one on the headline shape (and much slower on causal shapes).
-# Likewise the mix of polynomial and special-function exponentials (POLY 1..4), also measured slower.
-EXTRA_VARIANTS = (
-    {"KIND": 2, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},
-    {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},
-    {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 16},  # packed fp16 exponentials: the unit needs two passes for them, no gain
-    {"KIND": 3, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # two softmax threads per row, 64 keys each
-    {"KIND": 3, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},   # ... 80 keys on the special-function unit, 48 on the polynomial
-    {"KIND": 4, "BLOCK_N": 128, "STAGES": 4, "POLY": 2},   # correction group takes keys [96,128) of every tile on the polynomial
-    {"KIND": 4, "BLOCK_N": 128, "STAGES": 4, "POLY": 1},   # ... keys [80,128)
-)
 
 
 def _seq_class(seq_len: int, units: int) -> str:
@@ -135,7 +124,7 @@ def prebuild(head_dims=SUPPORTED_HEAD_DIMS, prune: bool = False):
     from ..jit.compiler import get_cache_dir
     paths = []
     for d in head_dims:
-        for point in (*tuning_space(d), *(() if os.getenv("FRAY_ATTN_FORCE") else EXTRA_VARIANTS)):
+        for point in tuning_space(d):
             keys = {"D": d, **point}
             code = generate(includes, arg_defs, cpp_format(template, keys), cpp_format(epilogue, keys))
             paths.append(build("flash_attn_cute", arg_defs, code).path)

@@ -21,10 +21,10 @@ MAX_DIFF = 1e-5
 
 
 def all_variants():
-    from fray_b200.jit_kernels.flashattn_cute import EXTRA_VARIANTS, tuning_space
+    from fray_b200.jit_kernels.flashattn_cute import tuning_space
     old = os.environ.pop("FRAY_ATTN_FORCE", None)
     try:
-        pts = {tuple(sorted(p.items())) for d in (64, 128) for p in (*tuning_space(d), *EXTRA_VARIANTS)}
+        pts = {tuple(sorted(p.items())) for d in (64, 128) for p in tuning_space(d)}
     finally:
         if old is not None:
             os.environ["FRAY_ATTN_FORCE"] = old
