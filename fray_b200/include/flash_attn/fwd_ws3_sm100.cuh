@@ -11,9 +11,10 @@
 //   warps 0-3   softmax group 0: KV steps 0, 2, 4, ... of the tile (thread r owns row r)
 //   warps 4-7   softmax group 1: KV steps 1, 3, 5, ... of the same rows
 //   warps 8-11  correction group: rescales O when the exponent offset moved; epilogue
-//   warp 12     MMA issue (leader CTA only when paired)
-//   warp 13     TMA producer (Q once, then K and V tiles through a ring of STAGES buffers)
-//   warps 14-15 idle (complete the warpgroup for setmaxnreg)
+//   warp 12     issues S(j) = Q.K_j^T          (leader CTA only when paired)
+//   warp 13     TMA producer for Q and the K ring
+//   warp 14     issues O += P(j).V_j           (leader CTA only when paired)
+//   warp 15     TMA producer for the V ring
 //
 // Tensor memory (512 columns): S buffers at [0,128) [128,256) [256,384), O at [384, 384 + D).  Step j
 // uses buffer j % 3; P(j) (16 bit) overwrites the first 64 columns of its buffer and is the A operand of
@@ -23,9 +24,11 @@
 // groups work on S(j) and S(j+1), so a group finds its next scores waiting and runs its steps back
 // to back; the two groups stay half a step apart and share the special-function unit evenly.
 //
-// Issue order in the MMA warp:  S(0) S(1) | S(2) PV(0) | S(3) PV(1) | ...  (S(j+3) reuses the buffer
-// of P(j): the tensor pipe executes in issue order, so it may be issued right behind PV(j)).
-// Ring order of the copies is the same: K0 K1 | K2 V0 | K3 V1 | ...
+// The two products are issued by two warps with a ring of K tiles and a ring of V tiles of their
+// own.  An issuing thread is held while the tensor pipe's short queue is full and spends a few hundred
+// cycles per step on its barriers; with one issuing warp the pipe ran dry during those (measured: 2070
+// cycles per step for 1024 cycles of tensor work), with two one of them always has work queued.
+// S(j+3) reuses the buffer of P(j): its warp waits for P.V(j) to complete (s_free).
 //
 // The two groups share the row state through shared memory: the group of step j reads the offset
 // m(j-1) the other group published, decides m(j) (lazily: it moves only when the row max grew by
@@ -48,7 +51,9 @@ struct Ws3Cfg {
   static_assert(D == 64 || D == 128, "head dim must be 64 or 128");
   static_assert(CTAS == 1 || CTAS == 2, "one CTA or a pair");
   static_assert(CTAS == 1 || D == 128, "the paired kernel splits V into two 64-dim halves");
-  static_assert(STAGES >= 3 && STAGES <= 12, "3..12 K/V buffers");
+  static_assert(STAGES >= 4 && STAGES <= 12, "4..12 K/V buffers in total");
+  static constexpr int kKStages = (STAGES + 1) / 2;        // K tiles in flight (S runs two steps ahead of P.V)
+  static constexpr int kVStages = STAGES / 2;
   static constexpr int BM = 128, BN = 128;
   static constexpr int kThreads = 512;
   static constexpr int kPanels = D / 64;                   // 64-element (128-byte) column panels of Q, K, O
@@ -63,7 +68,7 @@ struct Ws3Cfg {
   static constexpr int kOffQ = 0;
   static constexpr int kOffKV = kQTileBytes;
   static constexpr int kOffBars = kOffKV + STAGES * kSlotBytes;
-  static constexpr int kNumBars = 1 + 2 * STAGES + 3 + 12 + 2 + 4 + 4 + 8 + 1;
+  static constexpr int kNumBars = 1 + 2 * STAGES + 3 + 3 + 12 + 2 + 4 + 4 + 8 + 1;
   static constexpr int kOffStats = ((kOffBars + kNumBars * 8 + 16 + 127) / 128) * 128;
   static constexpr int kStatsBytes = (4 + 2 + 2 + 2) * 128 * 4;  // alpha[4], m_hand[2], l_fin[2], m_fin[2] x 128 rows
 #ifdef FRAY_ATTN_TRACE
@@ -90,7 +95,7 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t p_bar, uint
                                               uint64_t* hand_other, uint32_t hand_parity, bool first_step,
                                               bool need_mask, int kv0, int row, int seq_k, int causal,
                                               float scale_log2, int lane, float& m_mine, float& l_run,
-                                              volatile uint32_t* abort_flag, int step) {
+                                              volatile uint32_t* abort_flag, int step, unsigned int* tr = nullptr) {
   auto load_half = [&](uint32_t (&h)[64], int half) {
     tmem_ld_x32(t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(h[0]));
     tmem_ld_x32(t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(h[32]));
@@ -125,6 +130,7 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t p_bar, uint
     }
   }
   const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+  FRAY_SM_TRACE(tr, 1);
   float m_j;
   if (first_step) {
     m_j = mx;
@@ -155,6 +161,7 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t p_bar, uint
     m_mine = m_j;
   }
   const float neg_m = (m_j == -INFINITY) ? 0.f : -m_j * scale_log2;
+  FRAY_SM_TRACE(tr, 3);
 
   float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
   auto exp_half = [&](uint32_t (&h)[64]) {
@@ -193,6 +200,7 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t p_bar, uint
   load_half(sb2, 1);  // second half again; it sits at columns [64,128), clear of the P chunks below
   exp_half(sa);
   store_publish(sa, 0, 0);
+  FRAY_SM_TRACE(tr, 9);
   store_publish(sa, 32, 1);
   tmem_wait_ld();
   if (need_mask) mask_half(sb2, 1);
@@ -213,16 +221,20 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
   uint8_t* q_smem = smem + Cfg::kOffQ;    // reused for the O tile at the end
-  uint8_t* kv_smem = smem + Cfg::kOffKV;  // ring slot s at kv_smem + s * kSlotBytes
+  uint8_t* k_smem = smem + Cfg::kOffKV;                    // K ring slot s at k_smem + s * kSlotBytes
+  uint8_t* v_smem = k_smem + Cfg::kKStages * Cfg::kSlotBytes;  // V ring behind it
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
-  uint64_t* q_full = bars;                    // [1]       producer(s) -> MMA
-  uint64_t* kv_full = q_full + 1;             // [STAGES]  producer(s) -> MMA
-  uint64_t* kv_empty = kv_full + STAGES;      // [STAGES]  MMA -> producer
-  uint64_t* s_full = kv_empty + STAGES;       // [3]       MMA -> softmax   (S(j) complete in buffer j % 3)
-  uint64_t* p_full = s_full + 3;              // [3][4]    softmax -> MMA   (chunk c of P(j) stored)
-  uint64_t* o_full = p_full + 12;             // [2]       MMA -> correction (PV(j) complete, barrier j & 1)
+  uint64_t* q_full = bars;                    // [1]         producer(s) -> QK warp
+  uint64_t* k_full = q_full + 1;              // [kKStages]  K producer(s) -> QK warp
+  uint64_t* k_empty = k_full + Cfg::kKStages; // [kKStages]  QK warp -> K producer
+  uint64_t* v_full = k_empty + Cfg::kKStages; // [kVStages]  V producer(s) -> PV warp
+  uint64_t* v_empty = v_full + Cfg::kVStages; // [kVStages]  PV warp -> V producer
+  uint64_t* s_full = v_empty + Cfg::kVStages; // [3]       QK warp -> softmax   (S(j) complete in buffer j % 3)
+  uint64_t* s_free = s_full + 3;              // [3]       PV warp -> QK warp   (P.V(j) complete: buffer j % 3 may be overwritten)
+  uint64_t* p_full = s_free + 3;              // [3][4]    softmax -> PV warp   (chunk c of P(j) stored)
+  uint64_t* o_full = p_full + 12;             // [2]       PV warp -> correction (PV(j) complete, barrier j & 1)
   uint64_t* corr_ready = o_full + 2;          // [4]       softmax -> correction (factor of step j >= 1 in slot (j - 1) & 3)
-  uint64_t* o_rescaled = corr_ready + 4;      // [4]       correction -> MMA (O ready for PV(j), slot (j - 1) & 3)
+  uint64_t* o_rescaled = corr_ready + 4;      // [4]       correction -> PV warp (O ready for PV(j), slot (j - 1) & 3)
   uint64_t* hand = o_rescaled + 4;            // [2][4]    softmax group g, warp w -> same warp of the other group
   uint64_t* fin = hand + 8;                   // [1]       softmax -> correction (partial row sums published)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
@@ -262,11 +274,8 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     FRAY_TRACE(6, 0, 0);
     *abort_flag = (*reinterpret_cast<volatile int*>(&fray_attn_status[0]) != 0) ? 2u : 0u;
     mbar_init(q_full, 1);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(kv_full + s, 1);
-      mbar_init(kv_empty + s, 1);
-    }
-    for (int i = 0; i < 3; ++i) mbar_init(s_full + i, 1);
+    for (int s = 0; s < 2 * STAGES; ++s) mbar_init(k_full + s, 1);  // k_full, k_empty, v_full, v_empty
+    for (int i = 0; i < 6; ++i) mbar_init(s_full + i, 1);           // s_full, s_free
     for (int i = 0; i < 12; ++i) mbar_init(p_full + i, 4 * CTAS);  // one arrival per softmax warp of every CTA
     mbar_init(o_full, 1);
     mbar_init(o_full + 1, 1);
@@ -324,10 +333,14 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, g, j);
       const int kv0 = j * BN;
       const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0));
+      unsigned int* tr = nullptr;
+#ifdef FRAY_ATTN_TRACE
+      if (trace_on && r == FRAY_TRACE_ROW && j < kTraceIters) tr = trace_sm + g * kTraceIters + j;
+#endif
       softmax_step3<CTAS>(tmem_base + buf * 128 + lane_base, p_full_addr + buf * 32, corr_ready + ((j - 1) & 3),
                           alpha_buf + ((j - 1) & 3) * 128 + r, m_hand + g * 128 + r, m_hand + (g ^ 1) * 128 + r,
                           hand + g * 4 + w, hand + (g ^ 1) * 4 + w, ((j - 1) >> 1) & 1, j == 0, need_mask, kv0, row,
-                          seq_k, causal, scale_log2, lane, m_mine, l_run, abort_flag, j);
+                          seq_k, causal, scale_log2, lane, m_mine, l_run, abort_flag, j, tr);
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, g, j);
       buf += 2;
       if (buf >= 3) {
@@ -393,11 +406,12 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
   } else {
     set_max_regs_dec<Cfg::kRegsOther>();
+    // With a pair, byte counts of both CTAs' copies are collected on the leader's barriers.
+    auto leader_addr = [&](uint64_t* bar) { return CTAS == 2 ? mapa_shared(smem_u32(bar), 0) : smem_u32(bar); };
     if (warp == 13 && lane == 0) {
-      // ============================================================= TMA producer
-      // With a pair, byte counts of both CTAs' copies are collected on the leader's barriers.
-      const uint32_t q_full_addr = CTAS == 2 ? mapa_shared(smem_u32(q_full), 0) : smem_u32(q_full);
-      const uint32_t kv_full_addr = CTAS == 2 ? mapa_shared(smem_u32(kv_full), 0) : smem_u32(kv_full);
+      // ============================================================= TMA producer: Q, then the K ring
+      const uint32_t q_full_addr = leader_addr(q_full);
+      const uint32_t k_full_addr = leader_addr(k_full);
       if (rank == 0) mbar_expect_tx(q_full, CTAS * Cfg::kQTileBytes);
 #pragma unroll
       for (int p = 0; p < Cfg::kPanels; ++p) {
@@ -409,77 +423,66 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       int slot = 0;
       uint32_t par = 0;  // parity of the ring's current round
-      auto fetch = [&](bool is_v, int jj) __attribute__((always_inline)) {
-        mbar_wait(kv_empty + slot, par ^ 1u, abort_flag, 0x401, jj);
-        if (*abort_flag == 0) {
-          if (rank == 0) mbar_expect_tx(kv_full + slot, CTAS * Cfg::kSlotBytes);
-          uint8_t* dst = kv_smem + slot * Cfg::kSlotBytes;
-          if (!is_v) {
+      for (int jj = 0; jj < n; ++jj) {
+        mbar_wait(k_empty + slot, par ^ 1u, abort_flag, 0x401, jj);
+        if (*abort_flag != 0) break;
+        if (rank == 0) mbar_expect_tx(k_full + slot, CTAS * Cfg::kSlotBytes);
+        uint8_t* dst = k_smem + slot * Cfg::kSlotBytes;
 #pragma unroll
-            for (int p = 0; p < Cfg::kPanels; ++p) {
-              if constexpr (CTAS == 1) {
-                tma_load_4d(dst + p * Cfg::kKPanelBytes, &tm_k, kv_full + slot, p * 64, jj * BN, h_kv, b);
-              } else {
-                tma_load_4d_pair(dst + p * Cfg::kKPanelBytes, &tm_k, kv_full_addr + slot * 8, p * 64,
-                                 jj * BN + static_cast<int>(rank) * Cfg::kKRows, h_kv, b);
-              }
-            }
+        for (int p = 0; p < Cfg::kPanels; ++p) {
+          if constexpr (CTAS == 1) {
+            tma_load_4d(dst + p * Cfg::kKPanelBytes, &tm_k, k_full + slot, p * 64, jj * BN, h_kv, b);
           } else {
-#pragma unroll
-            for (int p = 0; p < Cfg::kVPanels; ++p) {
-              if constexpr (CTAS == 1) {
-                tma_load_4d(dst + p * Cfg::kVPanelBytes, &tm_v, kv_full + slot, p * 64, jj * BN, h_kv, b);
-              } else {
-                tma_load_4d_pair(dst + p * Cfg::kVPanelBytes, &tm_v, kv_full_addr + slot * 8,
-                                 (static_cast<int>(rank) * Cfg::kVPanels + p) * 64, jj * BN, h_kv, b);
-              }
-            }
+            tma_load_4d_pair(dst + p * Cfg::kKPanelBytes, &tm_k, k_full_addr + slot * 8, p * 64,
+                             jj * BN + static_cast<int>(rank) * Cfg::kKRows, h_kv, b);
           }
         }
-        if (++slot == STAGES) {
+        if (++slot == Cfg::kKStages) {
           slot = 0;
           par ^= 1u;
         }
-      };
-      fetch(false, 0);
-      if (n > 1) fetch(false, 1);
-      for (int j = 0; j < n; ++j) {
-        if (j + 2 < n) fetch(false, j + 2);
-        fetch(true, j);
+      }
+    } else if (warp == 15 && lane == 0) {
+      // ============================================================= TMA producer: the V ring
+      const uint32_t v_full_addr = leader_addr(v_full);
+      int slot = 0;
+      uint32_t par = 0;
+      for (int jj = 0; jj < n; ++jj) {
+        mbar_wait(v_empty + slot, par ^ 1u, abort_flag, 0x402, jj);
+        if (*abort_flag != 0) break;
+        if (rank == 0) mbar_expect_tx(v_full + slot, CTAS * Cfg::kSlotBytes);
+        uint8_t* dst = v_smem + slot * Cfg::kSlotBytes;
+#pragma unroll
+        for (int p = 0; p < Cfg::kVPanels; ++p) {
+          if constexpr (CTAS == 1) {
+            tma_load_4d(dst + p * Cfg::kVPanelBytes, &tm_v, v_full + slot, p * 64, jj * BN, h_kv, b);
+          } else {
+            tma_load_4d_pair(dst + p * Cfg::kVPanelBytes, &tm_v, v_full_addr + slot * 8,
+                             (static_cast<int>(rank) * Cfg::kVPanels + p) * 64, jj * BN, h_kv, b);
+          }
+        }
+        if (++slot == Cfg::kVStages) {
+          slot = 0;
+          par ^= 1u;
+        }
       }
     } else if (warp == 12 && rank == 0) {
-      // ============================================================= MMA issue (whole warp, one elected lane issues)
-      constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);                 // K-major operand (Q, K)
-      constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kVPanelBytes, 1024);  // MN-major operand (V)
+      // ============================================================= S(j) = Q . K_j^T (whole warp, one elected lane issues)
+      constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);  // K-major operand (Q, K)
       constexpr uint32_t kDescKHi = static_cast<uint32_t>(kDescK >> 32), kDescKLo = static_cast<uint32_t>(kDescK);
-      constexpr uint32_t kDescVHi = static_cast<uint32_t>(kDescV >> 32), kDescVLo = static_cast<uint32_t>(kDescV);
       constexpr uint32_t kIdescQK = idesc_f16_f32(CTAS * Cfg::BM, BN, false, false);
-      constexpr uint32_t kIdescPV = idesc_f16_f32(CTAS * Cfg::BM, D, false, true);
       const uint32_t q_lo = kDescKLo | ((smem_u32(q_smem) & 0x3FFFF) >> 4);
-      const uint32_t kv_addr = smem_u32(kv_smem);
-      const int n_entries = 2 * n;
-      int slot = 0, entry = 0;
-      uint32_t par = 0;
-      auto wait_slot = [&](uint32_t site) __attribute__((always_inline)) {
-        if constexpr (CTAS == 1) {
-          mbar_wait(kv_full + slot, par, abort_flag, site, entry);
-        } else {
-          mbar_wait_cluster(kv_full + slot, par, abort_flag, site, entry);
-        }
+      const uint32_t k_addr = smem_u32(k_smem);
+      mbar_wait(q_full, 0, abort_flag, 0x511);
+      int slot = 0, buf = 0;
+      uint32_t par = 0, buf_par = 0;  // parities of the ring's round and of the buffer's use (jj / 3)
+      for (int jj = 0; jj < n; ++jj) {
+        mbar_wait(k_full + slot, par, abort_flag, 0x501, jj);
+        // the buffer's previous tenant P(jj - 3) has been consumed
+        if (jj >= 3) mbar_wait(s_free + buf, buf_par ^ 1u, abort_flag, 0x506, jj);
         tc_fence_after_sync();
-      };
-      auto release_slot = [&]() __attribute__((always_inline)) {
-        // the last STAGES entries are never refilled: no arrival may reach a CTA that has already left
-        if (entry + STAGES < n_entries) mma_commit_elect_g<CTAS>(kv_empty + slot);
-        ++entry;
-        if (++slot == STAGES) {
-          slot = 0;
-          par ^= 1u;
-        }
-      };
-      auto issue_qk = [&](int jj, int buf) __attribute__((always_inline)) {  // S(jj) = Q . K_jj^T
-        wait_slot(0x501);
-        const uint32_t k_lo = kDescKLo | (((kv_addr + slot * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
+        FRAY_TRACE(2, jj & 1, jj);
+        const uint32_t k_lo = kDescKLo | (((k_addr + slot * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
         const uint32_t t_s = tmem_base + buf * 128;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -488,28 +491,35 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           mma_ss_elect_g<CTAS>(t_s, q_lo + qoff, kDescKHi, k_lo + koff, kDescKHi, kIdescQK, kk > 0);
         }
         mma_commit_elect_g<CTAS>(s_full + buf);
-        release_slot();
+        // the last ring entries are never refilled: no arrival may reach a CTA that has already left
+        if (jj + Cfg::kKStages < n) mma_commit_elect_g<CTAS>(k_empty + slot);
         FRAY_TRACE(8, jj & 1, jj);
-      };
-      auto issue_pv = [&](int j, int buf, uint32_t p_par) __attribute__((always_inline)) {  // O (+)= P(j) . V_j
-        wait_slot(0x502);
-        if (j > 0) {
-          if constexpr (CTAS == 1) {
-            mbar_wait(o_rescaled + ((j - 1) & 3), ((j - 1) >> 2) & 1, abort_flag, 0x505, j);
-          } else {
-            mbar_wait_cluster(o_rescaled + ((j - 1) & 3), ((j - 1) >> 2) & 1, abort_flag, 0x505, j);
-          }
+        if (++slot == Cfg::kKStages) {
+          slot = 0;
+          par ^= 1u;
         }
-        const uint32_t v_lo = kDescVLo | (((kv_addr + slot * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
+        if (++buf == 3) {
+          buf = 0;
+          buf_par ^= 1u;
+        }
+      }
+    } else if (warp == 14 && rank == 0) {
+      // ============================================================= O (+)= P(j) . V_j (whole warp, one elected lane issues)
+      constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kVPanelBytes, 1024);  // MN-major operand (V)
+      constexpr uint32_t kDescVHi = static_cast<uint32_t>(kDescV >> 32), kDescVLo = static_cast<uint32_t>(kDescV);
+      constexpr uint32_t kIdescPV = idesc_f16_f32(CTAS * Cfg::BM, D, false, true);
+      const uint32_t v_addr = smem_u32(v_smem);
+      const uint32_t t_o = tmem_base + Cfg::kColO;
+      int slot = 0, buf = 0;
+      uint32_t par = 0, buf_par = 0;
+      for (int j = 0; j < n; ++j) {
+        mbar_wait(v_full + slot, par, abort_flag, 0x502, j);
+        if (j > 0) mbar_wait(o_rescaled + ((j - 1) & 3), ((j - 1) >> 2) & 1, abort_flag, 0x505, j);
+        const uint32_t v_lo = kDescVLo | (((v_addr + slot * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
         const uint32_t t_p = tmem_base + buf * 128;
-        const uint32_t t_o = tmem_base + Cfg::kColO;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          if constexpr (CTAS == 1) {
-            FRAY_CRIT_WAIT(p_full + buf * 4 + q, p_par, abort_flag, 0x503, j);
-          } else {
-            mbar_wait_cluster(p_full + buf * 4 + q, p_par, abort_flag, 0x503, j);
-          }
+          FRAY_CRIT_WAIT(p_full + buf * 4 + q, buf_par, abort_flag, 0x503, j);
           tc_fence_after_sync();
           if (q == 0) FRAY_TRACE(5, j & 1, j);
 #pragma unroll
@@ -519,27 +529,16 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           }
         }
         mma_commit_elect_g<CTAS>(o_full + (j & 1));
-        release_slot();
+        if (j + 3 < n) mma_commit_elect_g<CTAS>(s_free + buf);
+        if (j + Cfg::kVStages < n) mma_commit_elect_g<CTAS>(v_empty + slot);
         FRAY_TRACE(7, j & 1, j);
-      };
-
-      if constexpr (CTAS == 1) {
-        mbar_wait(q_full, 0, abort_flag, 0x511);
-      } else {
-        mbar_wait_cluster(q_full, 0, abort_flag, 0x511);
-      }
-      issue_qk(0, 0);
-      if (n > 1) issue_qk(1, 1);
-      int buf = 0;          // j % 3
-      uint32_t p_par = 0;   // (j / 3) & 1
-      for (int j = 0; j < n; ++j) {
-        int buf2 = buf + 2;
-        if (buf2 >= 3) buf2 -= 3;
-        if (j + 2 < n) issue_qk(j + 2, buf2);
-        issue_pv(j, buf, p_par);
+        if (++slot == Cfg::kVStages) {
+          slot = 0;
+          par ^= 1u;
+        }
         if (++buf == 3) {
           buf = 0;
-          p_par ^= 1u;
+          buf_par ^= 1u;
         }
       }
     }

@@ -191,39 +191,12 @@ __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr)
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on an mbarrier named by a cluster-wide address (this CTA's or the peer's).
+// Arrive on an mbarrier named by a cluster-wide address (this CTA's or the peer's).  Plain CTA-scope
+// release: what these arrivals hand over lives in tensor memory (ordered by the tcgen05 fences around
+// them) or was written by the copy engine (ordered by its own byte-count completion), never in generic
+// memory of the other CTA; a cluster-scope release was measured to cost ~700 cycles per arrival.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// Waits on a barrier of this CTA that threads of the peer CTA arrive on: acquire at cluster scope.
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
-      "selp.b32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-__device__ __forceinline__ void mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                                  uint32_t site, uint32_t extra = 0) {
-  if (mbar_try_wait_cluster(bar, parity)) return;
-  const long long t0 = clock64();
-  uint32_t polls = 0;
-  while (!mbar_try_wait_cluster(bar, parity)) {
-    if ((++polls & 31u) == 0u) {
-      if (*abort_flag) return;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        report_timeout(abort_flag, site, extra);
-        return;
-      }
-    }
-  }
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // ---------------------------------------------------------------- TMA
