@@ -6,15 +6,16 @@
 // owns 256 consecutive rows and every product is one M = 256 instruction issued by the pair's
 // leader: each CTA holds its own rows of Q, P, S and O and only HALF of every K and V tile (K: 64 of
 // the 128 keys, V: 64 of the 128 head dims), fetched by its own plain TMA copies, so the K/V
-// traffic per query row is that of a 256-row tile while each CTA's tensor memory holds 128 rows.
+// traffic per query row is that of a 256-row tile while each CTA's tensor memory holds 128 rows, and
+// the operand reads of a product take 96 instead of 128 bytes of shared-memory bandwidth per clock.
 //
 //   warps 0-3   softmax group 0: KV steps 0, 2, 4, ... of the tile (thread r owns row r)
 //   warps 4-7   softmax group 1: KV steps 1, 3, 5, ... of the same rows
 //   warps 8-11  correction group: rescales O when the exponent offset moved; epilogue
-//   warp 12     issues S(j) = Q.K_j^T          (leader CTA only when paired)
-//   warp 13     TMA producer for Q and the K ring
-//   warp 14     issues O += P(j).V_j           (leader CTA only when paired)
-//   warp 15     TMA producer for the V ring
+//   warp 12     MMA issue (leader CTA only when paired)
+//   warp 13     TMA producer for Q and the K ring (STAGES slots)
+//   warp 14     TMA producer for V (three slots, one per score buffer)
+//   warp 15     idle
 //
 // Tensor memory (512 columns): S buffers at [0,128) [128,256) [256,384), O at [384, 384 + D).  Step j
 // uses buffer j % 3; P(j) (16 bit) overwrites the first 64 columns of its buffer and is the A operand of
@@ -24,11 +25,12 @@
 // groups work on S(j) and S(j+1), so a group finds its next scores waiting and runs its steps back
 // to back; the two groups stay half a step apart and share the special-function unit evenly.
 //
-// The two products are issued by two warps with a ring of K tiles and a ring of V tiles of their
-// own.  An issuing thread is held while the tensor pipe's short queue is full and spends a few hundred
-// cycles per step on its barriers; with one issuing warp the pipe ran dry during those (measured: 2070
-// cycles per step for 1024 cycles of tensor work), with two one of them always has work queued.
-// S(j+3) reuses the buffer of P(j): its warp waits for P.V(j) to complete (s_free).
+// Issue order in the MMA warp:  S(0) S(1) | S(2) PV(0) | S(3) PV(1) | ...  S(j+3) reuses the buffer
+// of P(j): the tensor pipe executes in issue order, so it is simply issued behind PV(j).  (Two issuing
+// warps, one per product, were measured slower: the pipe handles alternating kinds of product badly.)
+// The issuing thread's own time is the scarce resource (a satisfied barrier wait costs it ~100 cycles
+// during which the pipe's short queue runs dry), so everything P.V(j) waits for arrives on ONE barrier:
+// the softmax warps that stored P(j), the correction warps that made O ready, and the bytes of V_j.
 //
 // The two groups share the row state through shared memory: the group of step j reads the offset
 // m(j-1) the other group published, decides m(j) (lazily: it moves only when the row max grew by
@@ -43,6 +45,13 @@
 #include "sm100_ptx.cuh"
 #include "softmax_tile_sm100.cuh"
 
+#ifndef FRAY_WS3_MODE
+#define FRAY_WS3_MODE 0
+#endif
+#ifndef FRAY_WS3_SKIP
+#define FRAY_WS3_SKIP 0  // timing experiments: 1 no MMA instructions, 2 no K/V copies (wrong results)
+#endif
+
 namespace fray {
 namespace sm100 {
 
@@ -51,9 +60,7 @@ struct Ws3Cfg {
   static_assert(D == 64 || D == 128, "head dim must be 64 or 128");
   static_assert(CTAS == 1 || CTAS == 2, "one CTA or a pair");
   static_assert(CTAS == 1 || D == 128, "the paired kernel splits V into two 64-dim halves");
-  static_assert(STAGES >= 4 && STAGES <= 12, "4..12 K/V buffers in total");
-  static constexpr int kKStages = (STAGES + 1) / 2;        // K tiles in flight (S runs two steps ahead of P.V)
-  static constexpr int kVStages = STAGES / 2;
+  static_assert(STAGES >= 2 && STAGES <= 8, "2..8 K buffers");
   static constexpr int BM = 128, BN = 128;
   static constexpr int kThreads = 512;
   static constexpr int kPanels = D / 64;                   // 64-element (128-byte) column panels of Q, K, O
@@ -64,11 +71,12 @@ struct Ws3Cfg {
   static constexpr int kVPanels = kPanels / CTAS;          // 64-dim panels of a V tile this CTA holds
   static constexpr int kVPanelBytes = BN * 128;
   static constexpr int kSlotBytes = kPanels * kKPanelBytes;
-  static_assert(kSlotBytes == kVPanels * kVPanelBytes, "K and V halves share the ring slots");
+  static_assert(kSlotBytes == kVPanels * kVPanelBytes, "K and V halves have the same size");
   static constexpr int kOffQ = 0;
-  static constexpr int kOffKV = kQTileBytes;
-  static constexpr int kOffBars = kOffKV + STAGES * kSlotBytes;
-  static constexpr int kNumBars = 1 + 2 * STAGES + 3 + 3 + 12 + 2 + 4 + 4 + 8 + 1;
+  static constexpr int kOffK = kQTileBytes;
+  static constexpr int kOffV = kOffK + STAGES * kSlotBytes;
+  static constexpr int kOffBars = kOffV + 3 * kSlotBytes;
+  static constexpr int kNumBars = 1 + 2 * STAGES + 3 + 3 + 3 + 4 + 8 + 1;
   static constexpr int kOffStats = ((kOffBars + kNumBars * 8 + 16 + 127) / 128) * 128;
   static constexpr int kStatsBytes = (4 + 2 + 2 + 2) * 128 * 4;  // alpha[4], m_hand[2], l_fin[2], m_fin[2] x 128 rows
 #ifdef FRAY_ATTN_TRACE
@@ -81,21 +89,28 @@ struct Ws3Cfg {
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kColO = 384;
   static constexpr int kRegsSoftmax = 184, kRegsCorrection = 80, kRegsOther = 64;
+  // arrivals on a "P.V(j) may start" barrier: softmax and correction warps of every CTA, and the
+  // leader's V producer (with the byte count of both CTAs' copies)
+  static constexpr int kPvReadyCount = 8 * CTAS + 1;
 };
 
 // One softmax step of one thread (= one query row) over the 128 scores at t_s.
-//   p_bar       address of the first of the buffer's four "P chunk stored" barriers (cluster-wide address of the
-//               leader's barriers when paired)
+//   pv_bar      barrier told that P of this step is stored (cluster-wide address of the leader's when paired)
 //   corr_bar / alpha_slot   where the factor for O of this step is published (not on a row's first step)
 //   m_pub / m_other         this group's and the other group's published offsets of the row
 //   hand_mine / hand_other  barriers (one arrival per warp) behind those two slots
-template <int CTAS>
-__device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t p_bar, uint64_t* corr_bar, float* alpha_slot,
+// MODE (bit set): 1 packed f32x2 arithmetic for the scaling and the row sum; 2 the second half's load runs
+// under the first half's row max; 4 all 128 scores stay in registers (no second fetch); 8 every fourth
+// pair of exponentials by polynomial on the FMA pipe instead of the special-function unit.
+template <int CTAS, int MODE = 0>
+__device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t pv_bar, uint64_t* corr_bar, float* alpha_slot,
                                               float* m_pub, const float* m_other, uint64_t* hand_mine,
                                               uint64_t* hand_other, uint32_t hand_parity, bool first_step,
                                               bool need_mask, int kv0, int row, int seq_k, int causal,
                                               float scale_log2, int lane, float& m_mine, float& l_run,
                                               volatile uint32_t* abort_flag, int step, unsigned int* tr = nullptr) {
+  constexpr bool kPacked = (MODE & 1) != 0, kOverlapLoad = (MODE & 2) != 0, kKeepAll = (MODE & 4) != 0;
+  constexpr bool kPoly = (MODE & 8) != 0;
   auto load_half = [&](uint32_t (&h)[64], int half) {
     tmem_ld_x32(t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(h[0]));
     tmem_ld_x32(t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(h[32]));
@@ -107,27 +122,67 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t p_bar, uint
       if (kv >= seq_k || (causal && kv > row)) h[c] = __float_as_uint(-INFINITY);
     }
   };
+  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+  auto max_half = [&](const uint32_t (&h)[64]) {
+#pragma unroll
+    for (int c = 0; c < 64; c += 8) {
+      mx0 = max3(mx0, __uint_as_float(h[c + 0]), __uint_as_float(h[c + 4]));
+      mx1 = max3(mx1, __uint_as_float(h[c + 1]), __uint_as_float(h[c + 5]));
+      mx2 = max3(mx2, __uint_as_float(h[c + 2]), __uint_as_float(h[c + 6]));
+      mx3 = max3(mx3, __uint_as_float(h[c + 3]), __uint_as_float(h[c + 7]));
+    }
+  };
 
   // The row is handled as two 64-key halves: both are loaded for the row max, the first stays in
-  // registers for its exponentials and the second is fetched again afterwards.
+  // registers for its exponentials and the second is fetched again afterwards (unless kKeepAll).
   uint32_t sa[64];
-  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-  {
+  uint32_t sb2[64];
+  float m_prev = -INFINITY;
+  auto fetch_m_prev = [&]() {
+    if (!first_step) {
+      // the other group decided the previous step's offset long ago: fetch it under the loads
+      mbar_wait(hand_other, hand_parity, abort_flag, 0x601, step);
+      m_prev = *m_other;
+    }
+  };
+  if constexpr (kKeepAll) {
+    load_half(sa, 0);
+    if constexpr (kOverlapLoad) {
+      fetch_m_prev();
+      tmem_wait_ld();
+      load_half(sb2, 1);
+      if (need_mask) mask_half(sa, 0);
+      max_half(sa);
+      tmem_wait_ld();
+    } else {
+      load_half(sb2, 1);
+      fetch_m_prev();
+      tmem_wait_ld();
+      if (need_mask) mask_half(sa, 0);
+      max_half(sa);
+    }
+    if (need_mask) mask_half(sb2, 1);
+    max_half(sb2);
+  } else {
     uint32_t sb[64];
     load_half(sa, 0);
-    load_half(sb, 1);
-    tmem_wait_ld();
-    if (need_mask) {
-      mask_half(sa, 0);
-      mask_half(sb, 1);
+    if constexpr (kOverlapLoad) {
+      fetch_m_prev();
+      tmem_wait_ld();
+      load_half(sb, 1);
+      if (need_mask) mask_half(sa, 0);
+      max_half(sa);
+      tmem_wait_ld();
+    } else {
+      load_half(sb, 1);
+      fetch_m_prev();
+      tmem_wait_ld();
+      if (need_mask) mask_half(sa, 0);
+      max_half(sa);
     }
-#pragma unroll
-    for (int c = 0; c < 64; c += 4) {
-      mx0 = max3(mx0, __uint_as_float(sa[c + 0]), __uint_as_float(sb[c + 0]));
-      mx1 = max3(mx1, __uint_as_float(sa[c + 1]), __uint_as_float(sb[c + 1]));
-      mx2 = max3(mx2, __uint_as_float(sa[c + 2]), __uint_as_float(sb[c + 2]));
-      mx3 = max3(mx3, __uint_as_float(sa[c + 3]), __uint_as_float(sb[c + 3]));
-    }
+    if (need_mask) mask_half(sb, 1);
+    max_half(sb);
+    load_half(sb2, 1);  // second half again; it sits at columns [64,128), clear of P (columns [0,64))
   }
   const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
   FRAY_SM_TRACE(tr, 1);
@@ -138,8 +193,6 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t p_bar, uint
     __syncwarp();
     if (lane == 0) mbar_arrive(hand_mine);
   } else {
-    mbar_wait(hand_other, hand_parity, abort_flag, 0x601, step);
-    const float m_prev = *m_other;
     const float m_new = fmaxf(mx, m_prev);
     float alpha = 1.f;
     m_j = m_prev;
@@ -164,50 +217,258 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t p_bar, uint
   FRAY_SM_TRACE(tr, 3);
 
   float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
-  auto exp_half = [&](uint32_t (&h)[64]) {
+  uint64_t rsp0 = 0ull, rsp1 = 0ull;  // packed partial row sums (two lanes each)
+  const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(neg_m, neg_m);
+  // exp2(S*c - m*c) of one 64-key half, rounded to 16 bit (the row sum takes the unrounded values)
+  // and stored as columns [col, col + 32) of P.
+  auto exp_store_half = [&](uint32_t (&h)[64], int col) {
+    uint32_t pk[32];
 #pragma unroll
-    for (int c = 0; c < 64; ++c) h[c] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(h[c]), scale_log2, neg_m)));
-  };
-  // Round 32 keys to 16 bit, add them to the row sum, store them as chunk q of P and hand the chunk
-  // to the MMA warp once the store has landed.
-  auto store_publish = [&](const uint32_t (&h)[64], int off, int q) {
-    uint32_t pk[16];
-#pragma unroll
-    for (int c = 0; c < 32; c += 4) {
-      const float p0 = __uint_as_float(h[off + c]), p1 = __uint_as_float(h[off + c + 1]);
-      const float p2 = __uint_as_float(h[off + c + 2]), p3 = __uint_as_float(h[off + c + 3]);
-      rs0 += p0;
-      rs1 += p1;
-      rs2 += p2;
-      rs3 += p3;
+    for (int c = 0; c < 64; c += 4) {
+      float p0, p1, p2, p3;
+      if constexpr (kPacked) {
+        const uint64_t xa = fma_f32x2(pack_f32x2(__uint_as_float(h[c + 0]), __uint_as_float(h[c + 1])), scale2, neg_m2);
+        const uint64_t xb = fma_f32x2(pack_f32x2(__uint_as_float(h[c + 2]), __uint_as_float(h[c + 3])), scale2, neg_m2);
+        uint64_t pa, pb;
+        float x0, x1, x2, x3;
+        unpack_f32x2(xa, x0, x1);
+        pa = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
+        if (kPoly && (c & 4) != 0) {
+          pb = ex2_poly_f32x2(xb);
+        } else {
+          unpack_f32x2(xb, x2, x3);
+          pb = pack_f32x2(ex2_approx(x2), ex2_approx(x3));
+        }
+        rsp0 = add_f32x2(rsp0, pa);
+        rsp1 = add_f32x2(rsp1, pb);
+        unpack_f32x2(pa, p0, p1);
+        unpack_f32x2(pb, p2, p3);
+      } else {
+        p0 = ex2_approx(fmaf(__uint_as_float(h[c + 0]), scale_log2, neg_m));
+        p1 = ex2_approx(fmaf(__uint_as_float(h[c + 1]), scale_log2, neg_m));
+        if (kPoly && (c & 4) != 0) {
+          ex2_poly_pair(fmaf(__uint_as_float(h[c + 2]), scale_log2, neg_m), fmaf(__uint_as_float(h[c + 3]), scale_log2, neg_m), p2, p3);
+        } else {
+          p2 = ex2_approx(fmaf(__uint_as_float(h[c + 2]), scale_log2, neg_m));
+          p3 = ex2_approx(fmaf(__uint_as_float(h[c + 3]), scale_log2, neg_m));
+        }
+        rs0 += p0;
+        rs1 += p1;
+        rs2 += p2;
+        rs3 += p3;
+      }
       pk[c >> 1] = pack_half2(p0, p1);
       pk[(c >> 1) + 1] = pack_half2(p2, p3);
     }
-    tmem_st_x16(t_s + q * 16, pk);
-    tmem_wait_st();
-    tc_fence_before_sync();
-    __syncwarp();
-    if (lane == 0) {
-      if constexpr (CTAS == 1) {
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(p_bar + q * 8) : "memory");
-      } else {
-        mbar_arrive_cluster(p_bar + q * 8);
-      }
+    tmem_st_x32(t_s + col, pk);
+  };
+  exp_store_half(sa, 0);
+  FRAY_SM_TRACE(tr, 9);
+  if constexpr (!kKeepAll) {
+    tmem_wait_ld();
+    if (need_mask) mask_half(sb2, 1);
+  }
+  exp_store_half(sb2, 32);
+  tmem_wait_st();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) {
+    if constexpr (CTAS == 1) {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pv_bar) : "memory");
+    } else {
+      mbar_arrive_cluster(pv_bar);
+    }
+  }
+  if constexpr (kPacked) {
+    unpack_f32x2(rsp0, rs0, rs1);
+    unpack_f32x2(rsp1, rs2, rs3);
+  }
+  l_run += (rs0 + rs1) + (rs2 + rs3);
+}
+
+// Row state a softmax thread carries from one of its steps to the next.
+struct SoftmaxRow {
+  float u_used = -INFINITY;  // exponent offset (in score units) baked into this group's partial row sum
+  float u_next = -INFINITY;  // offset this group would use next (raised lazily when the row max outgrew u_used)
+  float l = 0.f;             // partial row sum over this group's steps, relative to u_used
+};
+
+// One softmax step with a SPECULATIVE exponent offset.  The offset u of a step need not be the row
+// max: any value works for which exp2(s - u) fits 16 bits (s - u <= 15 in the scaled base-2 domain),
+// as long as O is rescaled by 2^(u(j-1) - u(j)) between consecutive steps and every partial row sum
+// knows its offset.  So a step takes the best guess available when it starts (its group's last offset
+// or the other group's hint, whichever is larger) and computes the exponentials right away, with the
+// row max evaluated alongside as filler for the issue slots the special-function unit leaves; the max
+// no longer sits between the loads and the exponentials, and nothing waits for the other group.
+// Afterwards the max is checked: if some row of the warp would overflow (rare: a score beat the
+// offset by more than 2^15) the warp repeats the step with the row max as that row's offset; if it
+// merely outgrew the offset by 2^8, the next steps are told to use the max (hint).  A row without an
+// offset yet (its first steps) gets one from a max-only pass first.
+//   u_slot      where the offset this step used is published for the correction group (it derives
+//               the factor for O from consecutive steps' offsets), signalled on corr_bar
+//   hint_mine / hint_other   the two groups' suggestions for the row's next offset
+// POLY: how many of every 4 pairs of exponentials are evaluated by polynomial on the FMA pipe.
+template <int CTAS, int POLY, int CHUNK = 32, bool PACKED = true>
+__device__ __forceinline__ void softmax_step_spec(uint32_t t_s, uint32_t pv_bar, uint64_t* corr_bar, float* u_slot,
+                                                  float* hint_mine, const float* hint_other, bool need_mask, int kv0,
+                                                  int row, int seq_k, int causal, float scale_log2, int lane,
+                                                  SoftmaxRow& st, unsigned int* tr = nullptr) {
+  static_assert(POLY >= 0 && POLY <= 2, "0, 1 or 2 of every 4 pairs by polynomial");
+  constexpr float kOverflow = 15.f;
+  auto mask_chunk = [&](uint32_t (&h)[32], int c0) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      const int kv = kv0 + c0 + c;
+      if (kv >= seq_k || (causal && kv > row)) h[c] = __float_as_uint(-INFINITY);
+    }
+  };
+  float mx0, mx1, mx2, mx3;
+  auto max_chunk = [&](const uint32_t (&h)[32]) {
+#pragma unroll
+    for (int c = 0; c < 32; c += 8) {
+      mx0 = max3(mx0, __uint_as_float(h[c + 0]), __uint_as_float(h[c + 4]));
+      mx1 = max3(mx1, __uint_as_float(h[c + 1]), __uint_as_float(h[c + 5]));
+      mx2 = max3(mx2, __uint_as_float(h[c + 2]), __uint_as_float(h[c + 6]));
+      mx3 = max3(mx3, __uint_as_float(h[c + 3]), __uint_as_float(h[c + 7]));
     }
   };
 
-  uint32_t sb2[64];
-  load_half(sb2, 1);  // second half again; it sits at columns [64,128), clear of the P chunks below
-  exp_half(sa);
-  store_publish(sa, 0, 0);
-  FRAY_SM_TRACE(tr, 9);
-  store_publish(sa, 32, 1);
-  tmem_wait_ld();
-  if (need_mask) mask_half(sb2, 1);
-  exp_half(sb2);
-  store_publish(sb2, 0, 2);
-  store_publish(sb2, 32, 3);
-  l_run += (rs0 + rs1) + (rs2 + rs3);
+  float u = fmaxf(st.u_next, *hint_other);
+  if (__any_sync(0xffffffffu, u == -INFINITY)) {
+    // some row of the warp has no offset yet: take its row max (the loads are warp-wide instructions)
+    mx0 = mx1 = mx2 = mx3 = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t h[32];
+      tmem_ld_x32(t_s + c * 32, h);
+      tmem_wait_ld();
+      if (need_mask) mask_chunk(h, c * 32);
+      max_chunk(h);
+    }
+    if (u == -INFINITY) u = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+  }
+  FRAY_SM_TRACE(tr, 1);
+
+  uint32_t pk[64];
+  float mx, rsum;
+#pragma unroll 1
+  for (int round = 0; round < 2; ++round) {  // the second round only after an overflow
+    const float neg_u = (u == -INFINITY) ? 0.f : -u * scale_log2;
+    const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_u2 = pack_f32x2(neg_u, neg_u);
+    uint64_t rsp0 = 0ull, rsp1 = 0ull;  // packed partial row sums
+    mx0 = mx1 = mx2 = mx3 = -INFINITY;
+    // 32 scores: row max alongside exp2(s*c - u*c), row sum from the unrounded values, 16-bit rounding
+    float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
+    auto process = [&](uint32_t (&h)[32], int c0) {
+      if (need_mask) mask_chunk(h, c0);
+      max_chunk(h);
+#pragma unroll
+      for (int c = 0; c < 32; c += 8) {
+        if constexpr (PACKED) {
+          uint64_t p[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(h[c + 2 * q]), __uint_as_float(h[c + 2 * q + 1])), scale2, neg_u2);
+            if (q >= 4 - POLY) {
+              p[q] = ex2_poly_f32x2(x);
+            } else {
+              float x0, x1;
+              unpack_f32x2(x, x0, x1);
+              p[q] = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
+            }
+          }
+          rsp0 = add_f32x2(rsp0, add_f32x2(p[0], p[2]));
+          rsp1 = add_f32x2(rsp1, add_f32x2(p[1], p[3]));
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float p0, p1;
+            unpack_f32x2(p[q], p0, p1);
+            pk[((c0 + c) >> 1) + q] = pack_half2(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float x0 = fmaf(__uint_as_float(h[c + 2 * q]), scale_log2, neg_u);
+            const float x1 = fmaf(__uint_as_float(h[c + 2 * q + 1]), scale_log2, neg_u);
+            float p0, p1;
+            if (q >= 4 - POLY) {
+              ex2_poly_pair(x0, x1, p0, p1);
+            } else {
+              p0 = ex2_approx(x0);
+              p1 = ex2_approx(x1);
+            }
+            if (q & 1) {
+              rs2 += p0;
+              rs3 += p1;
+            } else {
+              rs0 += p0;
+              rs1 += p1;
+            }
+            pk[((c0 + c) >> 1) + q] = pack_half2(p0, p1);
+          }
+        }
+      }
+    };
+    // the next chunk's load runs under the current chunk's arithmetic
+    uint32_t ha[32], hb[32];
+    if constexpr (CHUNK == 32) {
+      tmem_ld_x32(t_s, ha);
+      tmem_wait_ld();
+      tmem_ld_x32(t_s + 32, hb);
+      process(ha, 0);
+      tmem_wait_ld();
+      tmem_ld_x32(t_s + 64, ha);
+      process(hb, 32);
+      tmem_wait_ld();
+      tmem_ld_x32(t_s + 96, hb);
+      process(ha, 64);
+      tmem_wait_ld();
+      process(hb, 96);
+    } else {
+      uint32_t hc[32], hd[32];
+      tmem_ld_x32(t_s, ha);
+      tmem_ld_x32(t_s + 32, hb);
+      tmem_wait_ld();
+      tmem_ld_x32(t_s + 64, hc);
+      tmem_ld_x32(t_s + 96, hd);
+      process(ha, 0);
+      process(hb, 32);
+      tmem_wait_ld();
+      process(hc, 64);
+      process(hd, 96);
+    }
+    mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+    float r0, r1, r2, r3;
+    unpack_f32x2(rsp0, r0, r1);
+    unpack_f32x2(rsp1, r2, r3);
+    rsum = ((r0 + r1) + (r2 + r3)) + ((rs0 + rs1) + (rs2 + rs3));
+    const bool over = (mx - u) * scale_log2 > kOverflow;  // false for NaN (a fully masked row without offset)
+    if (!__any_sync(0xffffffffu, over)) break;
+    if (over) u = mx;
+  }
+  FRAY_SM_TRACE(tr, 3);
+  // bookkeeping: the partial row sum follows the offset; later steps are told when the max outgrew it
+  if (u != st.u_used) {
+    if (st.u_used != -INFINITY) st.l *= ex2_approx((st.u_used - u) * scale_log2);
+    st.u_used = u;
+  }
+  st.l += rsum;
+  st.u_next = ((mx - u) * scale_log2 > kRescaleThreshold) ? mx : u;
+  *u_slot = u;
+  *hint_mine = st.u_next;
+  tmem_st_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
+  tmem_st_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
+  tmem_wait_st();
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) {
+    mbar_arrive(corr_bar);
+    if constexpr (CTAS == 1) {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pv_bar) : "memory");
+    } else {
+      mbar_arrive_cluster(pv_bar);
+    }
+  }
 }
 
 template <int D, int STAGES, int CTAS>
@@ -220,23 +481,19 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  uint8_t* q_smem = smem + Cfg::kOffQ;    // reused for the O tile at the end
-  uint8_t* k_smem = smem + Cfg::kOffKV;                    // K ring slot s at k_smem + s * kSlotBytes
-  uint8_t* v_smem = k_smem + Cfg::kKStages * Cfg::kSlotBytes;  // V ring behind it
+  uint8_t* q_smem = smem + Cfg::kOffQ;  // reused for the O tile at the end
+  uint8_t* k_smem = smem + Cfg::kOffK;  // K ring slot s at k_smem + s * kSlotBytes
+  uint8_t* v_smem = smem + Cfg::kOffV;  // V of step j at v_smem + (j % 3) * kSlotBytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
-  uint64_t* q_full = bars;                    // [1]         producer(s) -> QK warp
-  uint64_t* k_full = q_full + 1;              // [kKStages]  K producer(s) -> QK warp
-  uint64_t* k_empty = k_full + Cfg::kKStages; // [kKStages]  QK warp -> K producer
-  uint64_t* v_full = k_empty + Cfg::kKStages; // [kVStages]  V producer(s) -> PV warp
-  uint64_t* v_empty = v_full + Cfg::kVStages; // [kVStages]  PV warp -> V producer
-  uint64_t* s_full = v_empty + Cfg::kVStages; // [3]       QK warp -> softmax   (S(j) complete in buffer j % 3)
-  uint64_t* s_free = s_full + 3;              // [3]       PV warp -> QK warp   (P.V(j) complete: buffer j % 3 may be overwritten)
-  uint64_t* p_full = s_free + 3;              // [3][4]    softmax -> PV warp   (chunk c of P(j) stored)
-  uint64_t* o_full = p_full + 12;             // [2]       PV warp -> correction (PV(j) complete, barrier j & 1)
-  uint64_t* corr_ready = o_full + 2;          // [4]       softmax -> correction (factor of step j >= 1 in slot (j - 1) & 3)
-  uint64_t* o_rescaled = corr_ready + 4;      // [4]       correction -> PV warp (O ready for PV(j), slot (j - 1) & 3)
-  uint64_t* hand = o_rescaled + 4;            // [2][4]    softmax group g, warp w -> same warp of the other group
-  uint64_t* fin = hand + 8;                   // [1]       softmax -> correction (partial row sums published)
+  uint64_t* q_full = bars;                // [1]       producer(s) -> MMA
+  uint64_t* k_full = q_full + 1;          // [STAGES]  K producer(s) -> MMA
+  uint64_t* k_empty = k_full + STAGES;    // [STAGES]  MMA -> K producer
+  uint64_t* s_full = k_empty + STAGES;    // [3]       MMA -> softmax: S(j) complete in buffer j % 3
+  uint64_t* pv_ready = s_full + 3;        // [3]       softmax + correction + V producer -> MMA: P.V(j) may start
+  uint64_t* pv_done = pv_ready + 3;       // [3]       MMA -> correction, V producer: P.V(j) complete
+  uint64_t* corr_ready = pv_done + 3;     // [4]       softmax -> correction: factor of step j >= 1 in slot (j - 1) & 3
+  uint64_t* hand = corr_ready + 4;        // [2][4]    softmax group g, warp w -> same warp of the other group
+  uint64_t* fin = hand + 8;               // [1]       softmax -> correction: partial row sums published
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
   float* alpha_buf = reinterpret_cast<float*>(smem + Cfg::kOffStats);  // [4][128]
@@ -274,15 +531,13 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     FRAY_TRACE(6, 0, 0);
     *abort_flag = (*reinterpret_cast<volatile int*>(&fray_attn_status[0]) != 0) ? 2u : 0u;
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2 * STAGES; ++s) mbar_init(k_full + s, 1);  // k_full, k_empty, v_full, v_empty
-    for (int i = 0; i < 6; ++i) mbar_init(s_full + i, 1);           // s_full, s_free
-    for (int i = 0; i < 12; ++i) mbar_init(p_full + i, 4 * CTAS);  // one arrival per softmax warp of every CTA
-    mbar_init(o_full, 1);
-    mbar_init(o_full + 1, 1);
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(corr_ready + i, 4);
-      mbar_init(o_rescaled + i, 4 * CTAS);
+    for (int s = 0; s < 2 * STAGES; ++s) mbar_init(k_full + s, 1);  // k_full, k_empty
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(s_full + i, 1);
+      mbar_init(pv_ready + i, Cfg::kPvReadyCount);
+      mbar_init(pv_done + i, 1);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(corr_ready + i, 4);
     for (int i = 0; i < 8; ++i) mbar_init(hand + i, 1);
     mbar_init(fin, 8);
     fence_barrier_init();
@@ -311,9 +566,8 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   if (tid == 0) FRAY_TRACE(6, 0, 1);
 
-  // Barriers that softmax / correction threads of both CTAs arrive on live in the leader.
-  const uint32_t p_full_addr = CTAS == 2 ? mapa_shared(smem_u32(p_full), 0) : smem_u32(p_full);
-  const uint32_t o_rescaled_addr = CTAS == 2 ? mapa_shared(smem_u32(o_rescaled), 0) : smem_u32(o_rescaled);
+  // Barriers that threads of both CTAs arrive on live in the leader.
+  auto leader_addr = [&](uint64_t* bar) { return CTAS == 2 ? mapa_shared(smem_u32(bar), 0) : smem_u32(bar); };
 
   if (warp < 8) {
     // =============================================================== softmax groups
@@ -323,6 +577,7 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int r = tid & 127;
     const int row = m0 + r;
     const uint32_t lane_base = static_cast<uint32_t>(w * 32) << 16;
+    const uint32_t pv_ready_addr = leader_addr(pv_ready);
     float m_mine = -INFINITY;  // offset this group's partial row sum refers to
     float l_run = 0.f;
     int buf = g;               // j % 3
@@ -337,7 +592,7 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #ifdef FRAY_ATTN_TRACE
       if (trace_on && r == FRAY_TRACE_ROW && j < kTraceIters) tr = trace_sm + g * kTraceIters + j;
 #endif
-      softmax_step3<CTAS>(tmem_base + buf * 128 + lane_base, p_full_addr + buf * 32, corr_ready + ((j - 1) & 3),
+      softmax_step3<CTAS, FRAY_WS3_MODE>(tmem_base + buf * 128 + lane_base, pv_ready_addr + buf * 8, corr_ready + ((j - 1) & 3),
                           alpha_buf + ((j - 1) & 3) * 128 + r, m_hand + g * 128 + r, m_hand + (g ^ 1) * 128 + r,
                           hand + g * 4 + w, hand + (g ^ 1) * 4 + w, ((j - 1) >> 1) & 1, j == 0, need_mask, kv0, row,
                           seq_k, causal, scale_log2, lane, m_mine, l_run, abort_flag, j, tr);
@@ -358,12 +613,26 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int r = tid & 127;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_o = tmem_base + Cfg::kColO + lane_base;
+    const uint32_t pv_ready_addr = leader_addr(pv_ready);
+    auto o_is_ready = [&](int buf) {
+      if (lane == 0) {
+        if constexpr (CTAS == 1) {
+          mbar_arrive(pv_ready + buf);
+        } else {
+          mbar_arrive_cluster(pv_ready_addr + buf * 8);
+        }
+      }
+    };
+    o_is_ready(0);  // step 0 overwrites O: nothing to rescale
+    int buf = 1;                 // j % 3
+    int pbuf = 0;                // (j - 1) % 3
+    uint32_t ppar = 0;           // ((j - 1) / 3) & 1
     for (int j = 1; j < n; ++j) {
       const int k = (j - 1) & 3;  // step 0 publishes no factor: step j is the slot's ((j - 1) / 4)-th use
       mbar_wait(corr_ready + k, ((j - 1) >> 2) & 1, abort_flag, 0x301, j);
       const float alpha = alpha_buf[k * 128 + r];
       if (__any_sync(0xffffffffu, alpha != 1.f)) {
-        mbar_wait(o_full + ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, 0x311, j);
+        mbar_wait(pv_done + pbuf, ppar, abort_flag, 0x311, j);  // P.V(j - 1) complete
         tc_fence_after_sync();
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -378,13 +647,10 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tc_fence_before_sync();
       }
       __syncwarp();
-      if (lane == 0) {
-        if constexpr (CTAS == 1) {
-          mbar_arrive(o_rescaled + k);
-        } else {
-          mbar_arrive_cluster(o_rescaled_addr + k * 8);
-        }
-      }
+      o_is_ready(buf);
+      pbuf = buf;
+      if (buf == 0) ppar ^= 1u;  // j just crossed a multiple of 3: so will j - 1 on the next turn
+      if (++buf == 3) buf = 0;
     }
     // Epilogue: the two groups' partial row sums, each relative to the offset of that group's last
     // step, are brought to the final offset (offsets never decrease) and added.
@@ -394,10 +660,10 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     float l = 0.f;
     if (m_a != -INFINITY) l += l_fin[r] * ex2_approx((m_a - m_f) * scale_log2);
     if (m_b != -INFINITY) l += l_fin[128 + r] * ex2_approx((m_b - m_f) * scale_log2);
-    mbar_wait(o_full + ((n - 1) & 1), ((n - 1) >> 1) & 1, abort_flag, 0x331, n);
+    mbar_wait(pv_done + (n - 1) % 3, ((n - 1) / 3) & 1, abort_flag, 0x331, n);
     tc_fence_after_sync();
     if (r == 0) FRAY_TRACE(6, 1, 0);
-    if (m0 < seq_len) {  // warp-uniform, CTA-uniform: a pair's second tile may lie past the last query
+    if (m0 < seq_len) {  // CTA-uniform: a pair's second tile may lie past the last query
       epilogue_tile<Cfg, D>(t_o, q_smem, r, l, m_f, &tm_o, m0, h, b, num_heads, seq_len, scale_log2, lse, 1);
       if (r == 0) {
         tma_store_wait_read();
@@ -406,10 +672,9 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     }
   } else {
     set_max_regs_dec<Cfg::kRegsOther>();
-    // With a pair, byte counts of both CTAs' copies are collected on the leader's barriers.
-    auto leader_addr = [&](uint64_t* bar) { return CTAS == 2 ? mapa_shared(smem_u32(bar), 0) : smem_u32(bar); };
     if (warp == 13 && lane == 0) {
       // ============================================================= TMA producer: Q, then the K ring
+      // With a pair, byte counts of both CTAs' copies are collected on the leader's barriers.
       const uint32_t q_full_addr = leader_addr(q_full);
       const uint32_t k_full_addr = leader_addr(k_full);
       if (rank == 0) mbar_expect_tx(q_full, CTAS * Cfg::kQTileBytes);
@@ -426,10 +691,14 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       for (int jj = 0; jj < n; ++jj) {
         mbar_wait(k_empty + slot, par ^ 1u, abort_flag, 0x401, jj);
         if (*abort_flag != 0) break;
-        if (rank == 0) mbar_expect_tx(k_full + slot, CTAS * Cfg::kSlotBytes);
+        if (FRAY_WS3_SKIP & 2) {
+          if (rank == 0) mbar_arrive(k_full + slot);
+        } else if (rank == 0) {
+          mbar_expect_tx(k_full + slot, CTAS * Cfg::kSlotBytes);
+        }
         uint8_t* dst = k_smem + slot * Cfg::kSlotBytes;
 #pragma unroll
-        for (int p = 0; p < Cfg::kPanels; ++p) {
+        for (int p = 0; p < ((FRAY_WS3_SKIP & 2) ? 0 : Cfg::kPanels); ++p) {
           if constexpr (CTAS == 1) {
             tma_load_4d(dst + p * Cfg::kKPanelBytes, &tm_k, k_full + slot, p * 64, jj * BN, h_kv, b);
           } else {
@@ -437,49 +706,56 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                              jj * BN + static_cast<int>(rank) * Cfg::kKRows, h_kv, b);
           }
         }
-        if (++slot == Cfg::kKStages) {
+        if (++slot == STAGES) {
           slot = 0;
           par ^= 1u;
         }
       }
-    } else if (warp == 15 && lane == 0) {
-      // ============================================================= TMA producer: the V ring
-      const uint32_t v_full_addr = leader_addr(v_full);
-      int slot = 0;
-      uint32_t par = 0;
-      for (int jj = 0; jj < n; ++jj) {
-        mbar_wait(v_empty + slot, par ^ 1u, abort_flag, 0x402, jj);
+    } else if (warp == 14 && lane == 0) {
+      // ============================================================= TMA producer: V_j into slot j % 3
+      // Its bytes are counted on the step's "P.V may start" barrier.
+      const uint32_t pv_ready_addr = leader_addr(pv_ready);
+      int buf = 0;
+      uint32_t par = 0;  // (j / 3) & 1
+      for (int j = 0; j < n; ++j) {
+        if (j >= 3) mbar_wait(pv_done + buf, par ^ 1u, abort_flag, 0x402, j);  // P.V(j - 3) has left the slot
         if (*abort_flag != 0) break;
-        if (rank == 0) mbar_expect_tx(v_full + slot, CTAS * Cfg::kSlotBytes);
-        uint8_t* dst = v_smem + slot * Cfg::kSlotBytes;
+        if (FRAY_WS3_SKIP & 2) {
+          if (rank == 0) mbar_arrive(pv_ready + buf);
+        } else if (rank == 0) {
+          mbar_expect_tx(pv_ready + buf, CTAS * Cfg::kSlotBytes);
+        }
+        uint8_t* dst = v_smem + buf * Cfg::kSlotBytes;
 #pragma unroll
-        for (int p = 0; p < Cfg::kVPanels; ++p) {
+        for (int p = 0; p < ((FRAY_WS3_SKIP & 2) ? 0 : Cfg::kVPanels); ++p) {
           if constexpr (CTAS == 1) {
-            tma_load_4d(dst + p * Cfg::kVPanelBytes, &tm_v, v_full + slot, p * 64, jj * BN, h_kv, b);
+            tma_load_4d(dst + p * Cfg::kVPanelBytes, &tm_v, pv_ready + buf, p * 64, j * BN, h_kv, b);
           } else {
-            tma_load_4d_pair(dst + p * Cfg::kVPanelBytes, &tm_v, v_full_addr + slot * 8,
-                             (static_cast<int>(rank) * Cfg::kVPanels + p) * 64, jj * BN, h_kv, b);
+            tma_load_4d_pair(dst + p * Cfg::kVPanelBytes, &tm_v, pv_ready_addr + buf * 8,
+                             (static_cast<int>(rank) * Cfg::kVPanels + p) * 64, j * BN, h_kv, b);
           }
         }
-        if (++slot == Cfg::kVStages) {
-          slot = 0;
+        if (++buf == 3) {
+          buf = 0;
           par ^= 1u;
         }
       }
     } else if (warp == 12 && rank == 0) {
-      // ============================================================= S(j) = Q . K_j^T (whole warp, one elected lane issues)
-      constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);  // K-major operand (Q, K)
+      // ============================================================= MMA issue (whole warp, one elected lane issues)
+      constexpr uint64_t kDescK = smem_desc_sw128(16, 1024);                 // K-major operand (Q, K)
+      constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kVPanelBytes, 1024);  // MN-major operand (V)
       constexpr uint32_t kDescKHi = static_cast<uint32_t>(kDescK >> 32), kDescKLo = static_cast<uint32_t>(kDescK);
+      constexpr uint32_t kDescVHi = static_cast<uint32_t>(kDescV >> 32), kDescVLo = static_cast<uint32_t>(kDescV);
       constexpr uint32_t kIdescQK = idesc_f16_f32(CTAS * Cfg::BM, BN, false, false);
+      constexpr uint32_t kIdescPV = idesc_f16_f32(CTAS * Cfg::BM, D, false, true);
       const uint32_t q_lo = kDescKLo | ((smem_u32(q_smem) & 0x3FFFF) >> 4);
       const uint32_t k_addr = smem_u32(k_smem);
-      mbar_wait(q_full, 0, abort_flag, 0x511);
-      int slot = 0, buf = 0;
-      uint32_t par = 0, buf_par = 0;  // parities of the ring's round and of the buffer's use (jj / 3)
-      for (int jj = 0; jj < n; ++jj) {
-        mbar_wait(k_full + slot, par, abort_flag, 0x501, jj);
-        // the buffer's previous tenant P(jj - 3) has been consumed
-        if (jj >= 3) mbar_wait(s_free + buf, buf_par ^ 1u, abort_flag, 0x506, jj);
+      const uint32_t v_addr = smem_u32(v_smem);
+      const uint32_t t_o = tmem_base + Cfg::kColO;
+      int slot = 0;
+      uint32_t k_par = 0;
+      auto issue_qk = [&](int jj, int buf) __attribute__((always_inline)) {  // S(jj) = Q . K_jj^T into buffer jj % 3
+        mbar_wait(k_full + slot, k_par, abort_flag, 0x501, jj);
         tc_fence_after_sync();
         FRAY_TRACE(2, jj & 1, jj);
         const uint32_t k_lo = kDescKLo | (((k_addr + slot * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
@@ -488,57 +764,43 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
           const uint32_t koff = ((kk >> 2) * Cfg::kKPanelBytes + (kk & 3) * 32) >> 4;
-          mma_ss_elect_g<CTAS>(t_s, q_lo + qoff, kDescKHi, k_lo + koff, kDescKHi, kIdescQK, kk > 0);
+          if (!(FRAY_WS3_SKIP & 1)) mma_ss_elect_g<CTAS>(t_s, q_lo + qoff, kDescKHi, k_lo + koff, kDescKHi, kIdescQK, kk > 0);
         }
         mma_commit_elect_g<CTAS>(s_full + buf);
         // the last ring entries are never refilled: no arrival may reach a CTA that has already left
-        if (jj + Cfg::kKStages < n) mma_commit_elect_g<CTAS>(k_empty + slot);
+        if (jj + STAGES < n) mma_commit_elect_g<CTAS>(k_empty + slot);
         FRAY_TRACE(8, jj & 1, jj);
-        if (++slot == Cfg::kKStages) {
+        if (++slot == STAGES) {
           slot = 0;
-          par ^= 1u;
+          k_par ^= 1u;
         }
-        if (++buf == 3) {
-          buf = 0;
-          buf_par ^= 1u;
-        }
-      }
-    } else if (warp == 14 && rank == 0) {
-      // ============================================================= O (+)= P(j) . V_j (whole warp, one elected lane issues)
-      constexpr uint64_t kDescV = smem_desc_sw128(Cfg::kVPanelBytes, 1024);  // MN-major operand (V)
-      constexpr uint32_t kDescVHi = static_cast<uint32_t>(kDescV >> 32), kDescVLo = static_cast<uint32_t>(kDescV);
-      constexpr uint32_t kIdescPV = idesc_f16_f32(CTAS * Cfg::BM, D, false, true);
-      const uint32_t v_addr = smem_u32(v_smem);
-      const uint32_t t_o = tmem_base + Cfg::kColO;
-      int slot = 0, buf = 0;
-      uint32_t par = 0, buf_par = 0;
-      for (int j = 0; j < n; ++j) {
-        mbar_wait(v_full + slot, par, abort_flag, 0x502, j);
-        if (j > 0) mbar_wait(o_rescaled + ((j - 1) & 3), ((j - 1) >> 2) & 1, abort_flag, 0x505, j);
-        const uint32_t v_lo = kDescVLo | (((v_addr + slot * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
+      };
+      auto issue_pv = [&](int j, int buf, uint32_t par) __attribute__((always_inline)) {  // O (+)= P(j) . V_j
+        FRAY_CRIT_WAIT(pv_ready + buf, par, abort_flag, 0x503, j);
+        tc_fence_after_sync();
+        FRAY_TRACE(5, j & 1, j);
+        const uint32_t v_lo = kDescVLo | (((v_addr + buf * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
         const uint32_t t_p = tmem_base + buf * 128;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          FRAY_CRIT_WAIT(p_full + buf * 4 + q, buf_par, abort_flag, 0x503, j);
-          tc_fence_after_sync();
-          if (q == 0) FRAY_TRACE(5, j & 1, j);
-#pragma unroll
-          for (int s2 = 0; s2 < 2; ++s2) {
-            const int kk = q * 2 + s2;
-            mma_ts_elect_g<CTAS>(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
-          }
-        }
-        mma_commit_elect_g<CTAS>(o_full + (j & 1));
-        if (j + 3 < n) mma_commit_elect_g<CTAS>(s_free + buf);
-        if (j + Cfg::kVStages < n) mma_commit_elect_g<CTAS>(v_empty + slot);
+        for (int kk = 0; kk < BN / 16; ++kk)
+          if (!(FRAY_WS3_SKIP & 1)) mma_ts_elect_g<CTAS>(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
+        mma_commit_elect_g<CTAS>(pv_done + buf);
         FRAY_TRACE(7, j & 1, j);
-        if (++slot == Cfg::kVStages) {
-          slot = 0;
-          par ^= 1u;
-        }
+      };
+
+      mbar_wait(q_full, 0, abort_flag, 0x511);
+      issue_qk(0, 0);
+      if (n > 1) issue_qk(1, 1);
+      int buf = 0;        // j % 3
+      uint32_t par = 0;   // (j / 3) & 1
+      for (int j = 0; j < n; ++j) {
+        int buf2 = buf + 2;
+        if (buf2 >= 3) buf2 -= 3;
+        if (j + 2 < n) issue_qk(j + 2, buf2);
+        issue_pv(j, buf, par);
         if (++buf == 3) {
           buf = 0;
-          buf_par ^= 1u;
+          par ^= 1u;
         }
       }
     }

@@ -599,6 +599,30 @@ __device__ __forceinline__ void ex2_poly_pair(float x0, float x1, float& p0, flo
   p0 = ex2_poly(x0);
   p1 = ex2_poly(x1);
 }
+// 2^x for a packed pair on the FMA/ALU pipes: the same cubic as ex2_poly with the additions and the
+// Horner steps as packed f32x2 instructions (one issue slot per pair), the clamp and the exponent
+// insertion per element.
+__device__ __forceinline__ uint64_t ex2_poly_f32x2(uint64_t x2) {
+  float x0, x1;
+  unpack_f32x2(x2, x0, x1);
+  x0 = fmaxf(x0, -120.f);
+  x1 = fmaxf(x1, -120.f);
+  const uint64_t xc = pack_f32x2(x0, x1);
+  const uint64_t magic = pack_f32x2(12582912.f, 12582912.f);
+  const uint64_t neg_magic = pack_f32x2(-12582912.f, -12582912.f);
+  const uint64_t t = add_f32x2(xc, magic);                 // low mantissa bits hold round(x)
+  const uint64_t r = add_f32x2(t, neg_magic);              // round(x) as a float
+  const uint64_t f = fma_f32x2(r, pack_f32x2(-1.f, -1.f), xc);  // x - round(x) in [-0.5, 0.5]
+  uint64_t q = fma_f32x2(pack_f32x2(0.0551716685f, 0.0551716685f), f, pack_f32x2(0.2426111251f, 0.2426111251f));
+  q = fma_f32x2(q, f, pack_f32x2(0.6932609677f, 0.6932609677f));
+  q = fma_f32x2(q, f, pack_f32x2(0.9999280572f, 0.9999280572f));
+  float q0, q1, t0, t1;
+  unpack_f32x2(q, q0, q1);
+  unpack_f32x2(t, t0, t1);
+  const uint32_t e0 = __float_as_uint(q0) + (__float_as_uint(t0) << 23);
+  const uint32_t e1 = __float_as_uint(q1) + (__float_as_uint(t1) << 23);
+  return pack_f32x2(__uint_as_float(e0), __uint_as_float(e1));
+}
 // Two fp32 values rounded to nearest into a pair of the 16-bit operand type (fp16, or bf16 in a
 // bf16 build), low element first.
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {

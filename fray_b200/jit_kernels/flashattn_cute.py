@@ -84,12 +84,12 @@ def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
     space = [
         {"KIND": 1, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # warp-specialised, two tiles per CTA, whole 128-key steps
         {"KIND": 5, "BLOCK_N": 128, "STAGES": 4, "POLY": 0},   # ... 64-key steps in two score buffers per tile
-        {"KIND": 6, "BLOCK_N": 128, "STAGES": 5 if d == 128 else 6, "POLY": 0},   # one tile per CTA, three score buffers
+        {"KIND": 6, "BLOCK_N": 128, "STAGES": 2 if d == 128 else 4, "POLY": 0},   # one tile per CTA, three score buffers (STAGES: K ring)
         {"KIND": 0, "BLOCK_N": 128, "STAGES": 1, "POLY": 0},
         {"KIND": 0, "BLOCK_N": 64, "STAGES": 1, "POLY": 0},
     ]
     if d == 128:
-        space.insert(3, {"KIND": 7, "BLOCK_N": 128, "STAGES": 6, "POLY": 0})  # three score buffers on a CTA pair (cta_group::2)
+        space.insert(3, {"KIND": 7, "BLOCK_N": 128, "STAGES": 4, "POLY": 0})  # three score buffers on a CTA pair (cta_group::2)
     forced = os.getenv("FRAY_ATTN_FORCE")  # e.g. "KIND=0,BLOCK_N=64,STAGES=1"
     if forced:
         point = {"POLY": 0}
