@@ -1,6 +1,6 @@
 #pragma once
-// Warp-specialised attention forward for sm_100a with THREE score buffers per query tile, for one
-// CTA or a pair of CTAs (tcgen05 cta_group::2).
+// Warp-specialised attention forward for sm_100a with the scores and the probabilities of a query
+// tile in SEPARATE tensor-memory buffers, for one CTA or a pair of CTAs (tcgen05 cta_group::2).
 //
 // A CTA owns ONE 128-row query tile of one (batch, head) slice; with CTAS == 2 a cluster of two CTAs
 // owns 256 consecutive rows and every product is one M = 256 instruction issued by the pair's
@@ -14,23 +14,25 @@
 //   warps 8-11  correction group: rescales O when the exponent offset moved; epilogue
 //   warp 12     MMA issue (leader CTA only when paired)
 //   warp 13     TMA producer for Q and the K ring (STAGES slots)
-//   warp 14     TMA producer for V (three slots, one per score buffer)
+//   warp 14     TMA producer for V (three slots)
 //   warp 15     idle
 //
-// Tensor memory (512 columns): S buffers at [0,128) [128,256) [256,384), O at [384, 384 + D).  Step j
-// uses buffer j % 3; P(j) (16 bit) overwrites the first 64 columns of its buffer and is the A operand of
-// O += P(j).V(j).  Why three: with two tiles and two buffers (fwd_ws_sm100.cuh) the chain
-// softmax(j) -> P.V(j) -> S(j+1) -> softmax(j+1) of one tile bounds the step, because S(j+1) can only
-// follow P.V(j) into the buffer P(j) occupies.  Here S(j+2) goes into the third buffer while the two
-// groups work on S(j) and S(j+1), so a group finds its next scores waiting and runs its steps back
-// to back; the two groups stay half a step apart and share the special-function unit evenly.
+// Tensor memory (512 columns): S(j) at [0,128) or [128,256) (j & 1), P(j) (16 bit) at [256,320) or
+// [320,384), O at [384, 384 + D).  In the two-tile kernel (fwd_ws_sm100.cuh) P overwrites its S, so
+// S(j+1) of a tile can only follow P.V(j) and the chain softmax(j) -> P.V(j) -> S(j+1) -> softmax(j+1)
+// bounds the step.  Here a softmax thread pulls its whole row of S(j) into registers first and
+// releases the score buffer at once, so S(j+2) is computed while the group still works on step j
+// and the group finds its next scores waiting: the two groups run their steps back to back, half a
+// step apart, and share the special-function unit evenly.  P(j) goes to a buffer of its own, which
+// P.V(j-2) left a whole step earlier.
 //
-// Issue order in the MMA warp:  S(0) S(1) | S(2) PV(0) | S(3) PV(1) | ...  S(j+3) reuses the buffer
-// of P(j): the tensor pipe executes in issue order, so it is simply issued behind PV(j).  (Two issuing
-// warps, one per product, were measured slower: the pipe handles alternating kinds of product badly.)
-// The issuing thread's own time is the scarce resource (a satisfied barrier wait costs it ~100 cycles
-// during which the pipe's short queue runs dry), so everything P.V(j) waits for arrives on ONE barrier:
-// the softmax warps that stored P(j), the correction warps that made O ready, and the bytes of V_j.
+// Issue order in the MMA warp:  S(0) S(1) | S(2) PV(0) | S(3) PV(1) | ...  The issuing thread's own time
+// is the scarce resource (a satisfied barrier wait costs it ~100 cycles during which the pipe's short
+// queue runs dry; two issuing warps, one per product, were measured slower still: the pipe handles
+// alternating kinds of product badly), so each product waits on ONE barrier: S(j) on the one that
+// collects the bytes of K_j and the arrivals of the softmax warps that released the score buffer;
+// P.V(j) on the one that collects the softmax warps that stored P(j), the correction warps that made
+// O ready, and the bytes of V_j.
 //
 // The two groups share the row state through shared memory: the group of step j reads the offset
 // m(j-1) the other group published, decides m(j) (lazily: it moves only when the row max grew by
@@ -44,13 +46,6 @@
 #include "host_sm100.cuh"
 #include "sm100_ptx.cuh"
 #include "softmax_tile_sm100.cuh"
-
-#ifndef FRAY_WS3_MODE
-#define FRAY_WS3_MODE 0
-#endif
-#ifndef FRAY_WS3_SKIP
-#define FRAY_WS3_SKIP 0  // timing experiments: 1 no MMA instructions, 2 no K/V copies (wrong results)
-#endif
 
 namespace fray {
 namespace sm100 {
@@ -76,7 +71,7 @@ struct Ws3Cfg {
   static constexpr int kOffK = kQTileBytes;
   static constexpr int kOffV = kOffK + STAGES * kSlotBytes;
   static constexpr int kOffBars = kOffV + 3 * kSlotBytes;
-  static constexpr int kNumBars = 1 + 2 * STAGES + 3 + 3 + 3 + 4 + 8 + 1;
+  static constexpr int kNumBars = 1 + 2 * STAGES + 2 + 3 + 3 + 4 + 8 + 1;
   static constexpr int kOffStats = ((kOffBars + kNumBars * 8 + 16 + 127) / 128) * 128;
   static constexpr int kStatsBytes = (4 + 2 + 2 + 2) * 128 * 4;  // alpha[4], m_hand[2], l_fin[2], m_fin[2] x 128 rows
 #ifdef FRAY_ATTN_TRACE
@@ -87,33 +82,61 @@ struct Ws3Cfg {
 #endif
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of one CTA");
   static constexpr int kTmemCols = 512;
-  static constexpr uint32_t kColO = 384;
+  static constexpr uint32_t kColP = 256, kColO = 384;
   static constexpr int kRegsSoftmax = 184, kRegsCorrection = 80, kRegsOther = 64;
+  // arrivals on a "S(j) may start" barrier: the leader's K producer (with the byte count of both CTAs'
+  // copies) and the softmax warps of every CTA that released the score buffer (step j - 2)
+  static constexpr int kKFullCount = 4 * CTAS + 1;
   // arrivals on a "P.V(j) may start" barrier: softmax and correction warps of every CTA, and the
   // leader's V producer (with the byte count of both CTAs' copies)
   static constexpr int kPvReadyCount = 8 * CTAS + 1;
 };
 
-// One softmax step of one thread (= one query row) over the 128 scores at t_s.
-//   pv_bar      barrier told that P of this step is stored (cluster-wide address of the leader's when paired)
-//   corr_bar / alpha_slot   where the factor for O of this step is published (not on a row's first step)
-//   m_pub / m_other         this group's and the other group's published offsets of the row
-//   hand_mine / hand_other  barriers (one arrival per warp) behind those two slots
-// MODE (bit set): 1 packed f32x2 arithmetic for the scaling and the row sum; 2 the second half's load runs
-// under the first half's row max; 4 all 128 scores stay in registers (no second fetch); 8 every fourth
-// pair of exponentials by polynomial on the FMA pipe instead of the special-function unit.
-template <int CTAS, int MODE = 0>
-__device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t pv_bar, uint64_t* corr_bar, float* alpha_slot,
-                                              float* m_pub, const float* m_other, uint64_t* hand_mine,
-                                              uint64_t* hand_other, uint32_t hand_parity, bool first_step,
-                                              bool need_mask, int kv0, int row, int seq_k, int causal,
-                                              float scale_log2, int lane, float& m_mine, float& l_run,
-                                              volatile uint32_t* abort_flag, int step, unsigned int* tr = nullptr) {
-  constexpr bool kPacked = (MODE & 1) != 0, kOverlapLoad = (MODE & 2) != 0, kKeepAll = (MODE & 4) != 0;
-  constexpr bool kPoly = (MODE & 8) != 0;
+#ifndef FRAY_WS3_X
+#define FRAY_WS3_X 0  // timing experiments: 1 no masking code, 2 no P-buffer check, 4 no fence at the release
+#endif
+#ifndef FRAY_WS3_SKIP
+#define FRAY_WS3_SKIP 0  // timing experiments only (wrong results): 1 no MMA instructions, 2 no K/V copies
+#endif
+
+// Share of the exponentials evaluated by polynomial on the FMA pipe (of every 4 pairs).
+#ifndef FRAY_WS3_POLY
+#define FRAY_WS3_POLY 1
+#endif
+
+// Barriers and slots one softmax step touches (addresses are cluster-wide where the barrier lives in the
+// pair's leader).
+struct SoftmaxStepIo {
+  uint32_t t_s;            // tensor-memory address of this thread's lane at column 0 of S(j)
+  uint32_t t_p;            // ... of P(j)
+  uint32_t released_bar;   // told that S(j) is in registers (0: nothing waits for the buffer any more)
+  uint32_t pv_bar;         // told that P(j) is stored
+  uint64_t* p_free_bar;    // P.V(j - 2) complete: its P buffer may be overwritten (null on a group's first step)
+  uint32_t p_free_parity;
+  uint64_t* corr_bar;      // factor for O published (not on a row's first step)
+  float* alpha_slot;
+  float* m_pub;            // this group's published offset of the row
+  const float* m_other;    // the other group's
+  uint64_t* hand_mine;     // barriers (one arrival per warp) behind those two slots
+  uint64_t* hand_other;
+  uint32_t hand_parity;
+};
+
+// One softmax step of one thread (= one query row).  The 128 scores are pulled into registers in one
+// go and the score buffer is released right away; the rest works from registers.
+// POLY of every 4 pairs of exponentials are evaluated by polynomial on the FMA pipe: a 128 x 128 tile
+// needs the special-function unit (16 results per clock and SM) for exactly as long as the tensor
+// pipe needs for the tile's two products, so with every exponential on the unit the softmax can
+// never hide behind the tensor work.
+template <int CTAS, int POLY, bool MASK>
+__device__ __forceinline__ void softmax_step3(const SoftmaxStepIo& io, bool first_step, int kv0, int row,
+                                              int seq_k, int causal, float scale_log2, int lane, float& m_mine,
+                                              float& l_run, volatile uint32_t* abort_flag, int step,
+                                              unsigned int* tr = nullptr) {
+  static_assert(POLY >= 0 && POLY <= 2, "0, 1 or 2 of every 4 pairs by polynomial");
   auto load_half = [&](uint32_t (&h)[64], int half) {
-    tmem_ld_x32(t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(h[0]));
-    tmem_ld_x32(t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(h[32]));
+    tmem_ld_x32(io.t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(h[0]));
+    tmem_ld_x32(io.t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(h[32]));
   };
   auto mask_half = [&](uint32_t (&h)[64], int half) {
 #pragma unroll
@@ -133,65 +156,53 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t pv_bar, uin
     }
   };
 
-  // The row is handled as two 64-key halves: both are loaded for the row max, the first stays in
-  // registers for its exponentials and the second is fetched again afterwards (unless kKeepAll).
-  uint32_t sa[64];
-  uint32_t sb2[64];
-  float m_prev = -INFINITY;
-  auto fetch_m_prev = [&]() {
-    if (!first_step) {
-      // the other group decided the previous step's offset long ago: fetch it under the loads
-      mbar_wait(hand_other, hand_parity, abort_flag, 0x601, step);
-      m_prev = *m_other;
-    }
-  };
-  if constexpr (kKeepAll) {
-    load_half(sa, 0);
-    if constexpr (kOverlapLoad) {
-      fetch_m_prev();
-      tmem_wait_ld();
-      load_half(sb2, 1);
-      if (need_mask) mask_half(sa, 0);
-      max_half(sa);
-      tmem_wait_ld();
+  uint32_t sa[64], sb[64];
+  load_half(sa, 0);
+  load_half(sb, 1);
+#ifdef FRAY_TRACE_SM_DETAIL
+  FRAY_SM_TRACE(tr, 8);
+#endif
+  tmem_wait_ld();
+#ifdef FRAY_TRACE_SM_DETAIL
+  FRAY_SM_TRACE(tr, 5);
+#endif
+  tc_fence_before_sync();
+  __syncwarp();
+  if (lane == 0 && io.released_bar != 0) {  // S(j + 2) may overwrite the scores now
+    if constexpr (CTAS == 1) {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(io.released_bar) : "memory");
     } else {
-      load_half(sb2, 1);
-      fetch_m_prev();
-      tmem_wait_ld();
-      if (need_mask) mask_half(sa, 0);
-      max_half(sa);
+      mbar_arrive_cluster(io.released_bar);
     }
-    if (need_mask) mask_half(sb2, 1);
-    max_half(sb2);
-  } else {
-    uint32_t sb[64];
-    load_half(sa, 0);
-    if constexpr (kOverlapLoad) {
-      fetch_m_prev();
-      tmem_wait_ld();
-      load_half(sb, 1);
-      if (need_mask) mask_half(sa, 0);
-      max_half(sa);
-      tmem_wait_ld();
-    } else {
-      load_half(sb, 1);
-      fetch_m_prev();
-      tmem_wait_ld();
-      if (need_mask) mask_half(sa, 0);
-      max_half(sa);
-    }
-    if (need_mask) mask_half(sb, 1);
-    max_half(sb);
-    load_half(sb2, 1);  // second half again; it sits at columns [64,128), clear of P (columns [0,64))
   }
+#ifdef FRAY_TRACE_SM_DETAIL
+  FRAY_SM_TRACE(tr, 7);
+#endif
+  if constexpr (MASK) {
+    mask_half(sa, 0);
+    mask_half(sb, 1);
+  }
+  max_half(sa);
+  max_half(sb);
+  // Barrier tests behind the loads, not beside them: a wait issued while tensor-memory loads are in
+  // flight queues behind them (measured ~150 cycles per satisfied wait).
+  float m_prev = -INFINITY;
+  if (!first_step) {
+    // the other group decided the previous step's offset long ago
+    if (!(FRAY_WS3_X & 8)) mbar_wait(io.hand_other, io.hand_parity, abort_flag, 0x601, step);
+    m_prev = *io.m_other;
+  }
+  // P.V(j - 2) was issued a whole step ago; that it has left the P buffer is tested here and only looked
+  // at before the first store to the buffer
+  const bool p_free = (FRAY_WS3_X & 2) || io.p_free_bar == nullptr || mbar_test_wait(io.p_free_bar, io.p_free_parity);
   const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
   FRAY_SM_TRACE(tr, 1);
   float m_j;
   if (first_step) {
     m_j = mx;
-    *m_pub = m_j;
+    *io.m_pub = m_j;
     __syncwarp();
-    if (lane == 0) mbar_arrive(hand_mine);
+    if (lane == 0) mbar_arrive(io.hand_mine);
   } else {
     const float m_new = fmaxf(mx, m_prev);
     float alpha = 1.f;
@@ -200,12 +211,12 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t pv_bar, uin
       alpha = ex2_approx((m_prev - m_new) * scale_log2);
       m_j = m_new;
     }
-    *m_pub = m_j;
-    *alpha_slot = alpha;
+    *io.m_pub = m_j;
+    *io.alpha_slot = alpha;
     __syncwarp();
     if (lane == 0) {
-      mbar_arrive(hand_mine);
-      mbar_arrive(corr_bar);
+      mbar_arrive(io.hand_mine);
+      mbar_arrive(io.corr_bar);
     }
   }
   if (m_j != m_mine) {
@@ -216,259 +227,63 @@ __device__ __forceinline__ void softmax_step3(uint32_t t_s, uint32_t pv_bar, uin
   const float neg_m = (m_j == -INFINITY) ? 0.f : -m_j * scale_log2;
   FRAY_SM_TRACE(tr, 3);
 
-  float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
   uint64_t rsp0 = 0ull, rsp1 = 0ull;  // packed partial row sums (two lanes each)
   const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(neg_m, neg_m);
-  // exp2(S*c - m*c) of one 64-key half, rounded to 16 bit (the row sum takes the unrounded values)
-  // and stored as columns [col, col + 32) of P.
-  auto exp_store_half = [&](uint32_t (&h)[64], int col) {
+  // exp2(S*c - m*c) of one 64-key half, rounded to 16 bit (the row sum takes the unrounded values).
+  // Packed f32x2 arithmetic: one issue slot per pair.
+  auto exp_half = [&](uint32_t (&h)[64], uint32_t (&pk)[32]) {
+#pragma unroll
+    for (int c = 0; c < 64; c += 8) {
+      uint64_t p[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(h[c + 2 * q]), __uint_as_float(h[c + 2 * q + 1])), scale2, neg_m2);
+        if (q >= 4 - POLY) {
+          p[q] = ex2_poly_f32x2(x);
+        } else {
+          float x0, x1;
+          unpack_f32x2(x, x0, x1);
+          p[q] = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
+        }
+      }
+      rsp0 = add_f32x2(rsp0, add_f32x2(p[0], p[2]));
+      rsp1 = add_f32x2(rsp1, add_f32x2(p[1], p[3]));
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float p0, p1;
+        unpack_f32x2(p[q], p0, p1);
+        pk[(c >> 1) + q] = pack_half2(p0, p1);
+      }
+    }
+  };
+  {
     uint32_t pk[32];
-#pragma unroll
-    for (int c = 0; c < 64; c += 4) {
-      float p0, p1, p2, p3;
-      if constexpr (kPacked) {
-        const uint64_t xa = fma_f32x2(pack_f32x2(__uint_as_float(h[c + 0]), __uint_as_float(h[c + 1])), scale2, neg_m2);
-        const uint64_t xb = fma_f32x2(pack_f32x2(__uint_as_float(h[c + 2]), __uint_as_float(h[c + 3])), scale2, neg_m2);
-        uint64_t pa, pb;
-        float x0, x1, x2, x3;
-        unpack_f32x2(xa, x0, x1);
-        pa = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
-        if (kPoly && (c & 4) != 0) {
-          pb = ex2_poly_f32x2(xb);
-        } else {
-          unpack_f32x2(xb, x2, x3);
-          pb = pack_f32x2(ex2_approx(x2), ex2_approx(x3));
-        }
-        rsp0 = add_f32x2(rsp0, pa);
-        rsp1 = add_f32x2(rsp1, pb);
-        unpack_f32x2(pa, p0, p1);
-        unpack_f32x2(pb, p2, p3);
-      } else {
-        p0 = ex2_approx(fmaf(__uint_as_float(h[c + 0]), scale_log2, neg_m));
-        p1 = ex2_approx(fmaf(__uint_as_float(h[c + 1]), scale_log2, neg_m));
-        if (kPoly && (c & 4) != 0) {
-          ex2_poly_pair(fmaf(__uint_as_float(h[c + 2]), scale_log2, neg_m), fmaf(__uint_as_float(h[c + 3]), scale_log2, neg_m), p2, p3);
-        } else {
-          p2 = ex2_approx(fmaf(__uint_as_float(h[c + 2]), scale_log2, neg_m));
-          p3 = ex2_approx(fmaf(__uint_as_float(h[c + 3]), scale_log2, neg_m));
-        }
-        rs0 += p0;
-        rs1 += p1;
-        rs2 += p2;
-        rs3 += p3;
-      }
-      pk[c >> 1] = pack_half2(p0, p1);
-      pk[(c >> 1) + 1] = pack_half2(p2, p3);
-    }
-    tmem_st_x32(t_s + col, pk);
-  };
-  exp_store_half(sa, 0);
+    exp_half(sa, pk);
+    // first store to the P buffer: P.V(j - 2) must have read it (see above; it has, unless the other CTA
+    // of a pair lags by most of a step, and then this CTA has to wait for it anyway)
+    if (!p_free) mbar_wait_spin(io.p_free_bar, io.p_free_parity, abort_flag, 0x602, step);
+    tmem_st_x32(io.t_p, pk);
+  }
   FRAY_SM_TRACE(tr, 9);
-  if constexpr (!kKeepAll) {
-    tmem_wait_ld();
-    if (need_mask) mask_half(sb2, 1);
+  {
+    uint32_t pk[32];
+    exp_half(sb, pk);
+    tmem_st_x32(io.t_p + 32, pk);
   }
-  exp_store_half(sb2, 32);
   tmem_wait_st();
   tc_fence_before_sync();
   __syncwarp();
   if (lane == 0) {
     if constexpr (CTAS == 1) {
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pv_bar) : "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(io.pv_bar) : "memory");
     } else {
-      mbar_arrive_cluster(pv_bar);
+      mbar_arrive_cluster(io.pv_bar);
     }
   }
-  if constexpr (kPacked) {
-    unpack_f32x2(rsp0, rs0, rs1);
-    unpack_f32x2(rsp1, rs2, rs3);
-  }
-  l_run += (rs0 + rs1) + (rs2 + rs3);
-}
-
-// Row state a softmax thread carries from one of its steps to the next.
-struct SoftmaxRow {
-  float u_used = -INFINITY;  // exponent offset (in score units) baked into this group's partial row sum
-  float u_next = -INFINITY;  // offset this group would use next (raised lazily when the row max outgrew u_used)
-  float l = 0.f;             // partial row sum over this group's steps, relative to u_used
-};
-
-// One softmax step with a SPECULATIVE exponent offset.  The offset u of a step need not be the row
-// max: any value works for which exp2(s - u) fits 16 bits (s - u <= 15 in the scaled base-2 domain),
-// as long as O is rescaled by 2^(u(j-1) - u(j)) between consecutive steps and every partial row sum
-// knows its offset.  So a step takes the best guess available when it starts (its group's last offset
-// or the other group's hint, whichever is larger) and computes the exponentials right away, with the
-// row max evaluated alongside as filler for the issue slots the special-function unit leaves; the max
-// no longer sits between the loads and the exponentials, and nothing waits for the other group.
-// Afterwards the max is checked: if some row of the warp would overflow (rare: a score beat the
-// offset by more than 2^15) the warp repeats the step with the row max as that row's offset; if it
-// merely outgrew the offset by 2^8, the next steps are told to use the max (hint).  A row without an
-// offset yet (its first steps) gets one from a max-only pass first.
-//   u_slot      where the offset this step used is published for the correction group (it derives
-//               the factor for O from consecutive steps' offsets), signalled on corr_bar
-//   hint_mine / hint_other   the two groups' suggestions for the row's next offset
-// POLY: how many of every 4 pairs of exponentials are evaluated by polynomial on the FMA pipe.
-template <int CTAS, int POLY, int CHUNK = 32, bool PACKED = true>
-__device__ __forceinline__ void softmax_step_spec(uint32_t t_s, uint32_t pv_bar, uint64_t* corr_bar, float* u_slot,
-                                                  float* hint_mine, const float* hint_other, bool need_mask, int kv0,
-                                                  int row, int seq_k, int causal, float scale_log2, int lane,
-                                                  SoftmaxRow& st, unsigned int* tr = nullptr) {
-  static_assert(POLY >= 0 && POLY <= 2, "0, 1 or 2 of every 4 pairs by polynomial");
-  constexpr float kOverflow = 15.f;
-  auto mask_chunk = [&](uint32_t (&h)[32], int c0) {
-#pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      const int kv = kv0 + c0 + c;
-      if (kv >= seq_k || (causal && kv > row)) h[c] = __float_as_uint(-INFINITY);
-    }
-  };
-  float mx0, mx1, mx2, mx3;
-  auto max_chunk = [&](const uint32_t (&h)[32]) {
-#pragma unroll
-    for (int c = 0; c < 32; c += 8) {
-      mx0 = max3(mx0, __uint_as_float(h[c + 0]), __uint_as_float(h[c + 4]));
-      mx1 = max3(mx1, __uint_as_float(h[c + 1]), __uint_as_float(h[c + 5]));
-      mx2 = max3(mx2, __uint_as_float(h[c + 2]), __uint_as_float(h[c + 6]));
-      mx3 = max3(mx3, __uint_as_float(h[c + 3]), __uint_as_float(h[c + 7]));
-    }
-  };
-
-  float u = fmaxf(st.u_next, *hint_other);
-  if (__any_sync(0xffffffffu, u == -INFINITY)) {
-    // some row of the warp has no offset yet: take its row max (the loads are warp-wide instructions)
-    mx0 = mx1 = mx2 = mx3 = -INFINITY;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t h[32];
-      tmem_ld_x32(t_s + c * 32, h);
-      tmem_wait_ld();
-      if (need_mask) mask_chunk(h, c * 32);
-      max_chunk(h);
-    }
-    if (u == -INFINITY) u = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-  }
-  FRAY_SM_TRACE(tr, 1);
-
-  uint32_t pk[64];
-  float mx, rsum;
-#pragma unroll 1
-  for (int round = 0; round < 2; ++round) {  // the second round only after an overflow
-    const float neg_u = (u == -INFINITY) ? 0.f : -u * scale_log2;
-    const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_u2 = pack_f32x2(neg_u, neg_u);
-    uint64_t rsp0 = 0ull, rsp1 = 0ull;  // packed partial row sums
-    mx0 = mx1 = mx2 = mx3 = -INFINITY;
-    // 32 scores: row max alongside exp2(s*c - u*c), row sum from the unrounded values, 16-bit rounding
-    float rs0 = 0.f, rs1 = 0.f, rs2 = 0.f, rs3 = 0.f;
-    auto process = [&](uint32_t (&h)[32], int c0) {
-      if (need_mask) mask_chunk(h, c0);
-      max_chunk(h);
-#pragma unroll
-      for (int c = 0; c < 32; c += 8) {
-        if constexpr (PACKED) {
-          uint64_t p[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint64_t x = fma_f32x2(pack_f32x2(__uint_as_float(h[c + 2 * q]), __uint_as_float(h[c + 2 * q + 1])), scale2, neg_u2);
-            if (q >= 4 - POLY) {
-              p[q] = ex2_poly_f32x2(x);
-            } else {
-              float x0, x1;
-              unpack_f32x2(x, x0, x1);
-              p[q] = pack_f32x2(ex2_approx(x0), ex2_approx(x1));
-            }
-          }
-          rsp0 = add_f32x2(rsp0, add_f32x2(p[0], p[2]));
-          rsp1 = add_f32x2(rsp1, add_f32x2(p[1], p[3]));
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float p0, p1;
-            unpack_f32x2(p[q], p0, p1);
-            pk[((c0 + c) >> 1) + q] = pack_half2(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float x0 = fmaf(__uint_as_float(h[c + 2 * q]), scale_log2, neg_u);
-            const float x1 = fmaf(__uint_as_float(h[c + 2 * q + 1]), scale_log2, neg_u);
-            float p0, p1;
-            if (q >= 4 - POLY) {
-              ex2_poly_pair(x0, x1, p0, p1);
-            } else {
-              p0 = ex2_approx(x0);
-              p1 = ex2_approx(x1);
-            }
-            if (q & 1) {
-              rs2 += p0;
-              rs3 += p1;
-            } else {
-              rs0 += p0;
-              rs1 += p1;
-            }
-            pk[((c0 + c) >> 1) + q] = pack_half2(p0, p1);
-          }
-        }
-      }
-    };
-    // the next chunk's load runs under the current chunk's arithmetic
-    uint32_t ha[32], hb[32];
-    if constexpr (CHUNK == 32) {
-      tmem_ld_x32(t_s, ha);
-      tmem_wait_ld();
-      tmem_ld_x32(t_s + 32, hb);
-      process(ha, 0);
-      tmem_wait_ld();
-      tmem_ld_x32(t_s + 64, ha);
-      process(hb, 32);
-      tmem_wait_ld();
-      tmem_ld_x32(t_s + 96, hb);
-      process(ha, 64);
-      tmem_wait_ld();
-      process(hb, 96);
-    } else {
-      uint32_t hc[32], hd[32];
-      tmem_ld_x32(t_s, ha);
-      tmem_ld_x32(t_s + 32, hb);
-      tmem_wait_ld();
-      tmem_ld_x32(t_s + 64, hc);
-      tmem_ld_x32(t_s + 96, hd);
-      process(ha, 0);
-      process(hb, 32);
-      tmem_wait_ld();
-      process(hc, 64);
-      process(hd, 96);
-    }
-    mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-    float r0, r1, r2, r3;
-    unpack_f32x2(rsp0, r0, r1);
-    unpack_f32x2(rsp1, r2, r3);
-    rsum = ((r0 + r1) + (r2 + r3)) + ((rs0 + rs1) + (rs2 + rs3));
-    const bool over = (mx - u) * scale_log2 > kOverflow;  // false for NaN (a fully masked row without offset)
-    if (!__any_sync(0xffffffffu, over)) break;
-    if (over) u = mx;
-  }
-  FRAY_SM_TRACE(tr, 3);
-  // bookkeeping: the partial row sum follows the offset; later steps are told when the max outgrew it
-  if (u != st.u_used) {
-    if (st.u_used != -INFINITY) st.l *= ex2_approx((st.u_used - u) * scale_log2);
-    st.u_used = u;
-  }
-  st.l += rsum;
-  st.u_next = ((mx - u) * scale_log2 > kRescaleThreshold) ? mx : u;
-  *u_slot = u;
-  *hint_mine = st.u_next;
-  tmem_st_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(pk[0]));
-  tmem_st_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(pk[32]));
-  tmem_wait_st();
-  tc_fence_before_sync();
-  __syncwarp();
-  if (lane == 0) {
-    mbar_arrive(corr_bar);
-    if constexpr (CTAS == 1) {
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(pv_bar) : "memory");
-    } else {
-      mbar_arrive_cluster(pv_bar);
-    }
-  }
+  float r0, r1, r2, r3;
+  unpack_f32x2(rsp0, r0, r1);
+  unpack_f32x2(rsp1, r2, r3);
+  l_run += (r0 + r1) + (r2 + r3);
 }
 
 template <int D, int STAGES, int CTAS>
@@ -486,11 +301,11 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint8_t* v_smem = smem + Cfg::kOffV;  // V of step j at v_smem + (j % 3) * kSlotBytes
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
   uint64_t* q_full = bars;                // [1]       producer(s) -> MMA
-  uint64_t* k_full = q_full + 1;          // [STAGES]  K producer(s) -> MMA
+  uint64_t* k_full = q_full + 1;          // [STAGES]  K producer(s) + softmax -> MMA: S(j) may start (slot j % STAGES)
   uint64_t* k_empty = k_full + STAGES;    // [STAGES]  MMA -> K producer
-  uint64_t* s_full = k_empty + STAGES;    // [3]       MMA -> softmax: S(j) complete in buffer j % 3
-  uint64_t* pv_ready = s_full + 3;        // [3]       softmax + correction + V producer -> MMA: P.V(j) may start
-  uint64_t* pv_done = pv_ready + 3;       // [3]       MMA -> correction, V producer: P.V(j) complete
+  uint64_t* s_full = k_empty + STAGES;    // [2]       MMA -> softmax: S(j) complete in buffer j & 1
+  uint64_t* pv_ready = s_full + 2;        // [3]       softmax + correction + V producer -> MMA: P.V(j) may start (j % 3)
+  uint64_t* pv_done = pv_ready + 3;       // [3]       MMA -> correction, V producer, softmax: P.V(j) complete (j % 3)
   uint64_t* corr_ready = pv_done + 3;     // [4]       softmax -> correction: factor of step j >= 1 in slot (j - 1) & 3
   uint64_t* hand = corr_ready + 4;        // [2][4]    softmax group g, warp w -> same warp of the other group
   uint64_t* fin = hand + 8;               // [1]       softmax -> correction: partial row sums published
@@ -531,9 +346,12 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     FRAY_TRACE(6, 0, 0);
     *abort_flag = (*reinterpret_cast<volatile int*>(&fray_attn_status[0]) != 0) ? 2u : 0u;
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2 * STAGES; ++s) mbar_init(k_full + s, 1);  // k_full, k_empty
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(k_full + s, Cfg::kKFullCount);
+      mbar_init(k_empty + s, 1);
+    }
+    for (int i = 0; i < 2; ++i) mbar_init(s_full + i, 1);
     for (int i = 0; i < 3; ++i) {
-      mbar_init(s_full + i, 1);
       mbar_init(pv_ready + i, Cfg::kPvReadyCount);
       mbar_init(pv_done + i, 1);
     }
@@ -568,6 +386,13 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   // Barriers that threads of both CTAs arrive on live in the leader.
   auto leader_addr = [&](uint64_t* bar) { return CTAS == 2 ? mapa_shared(smem_u32(bar), 0) : smem_u32(bar); };
+  auto arrive_leader = [&](uint32_t addr) {
+    if constexpr (CTAS == 1) {
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
+    } else {
+      mbar_arrive_cluster(addr);
+    }
+  };
 
   if (warp < 8) {
     // =============================================================== softmax groups
@@ -577,13 +402,26 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int r = tid & 127;
     const int row = m0 + r;
     const uint32_t lane_base = static_cast<uint32_t>(w * 32) << 16;
+    const uint32_t k_full_addr = leader_addr(k_full);
     const uint32_t pv_ready_addr = leader_addr(pv_ready);
+    // both score buffers start out free: the arrivals S(0) and S(1) wait for besides their K tiles
+    if (lane == 0 && g < n) arrive_leader(k_full_addr + g * 8);
+    SoftmaxStepIo io;
+    io.t_s = tmem_base + g * 128 + lane_base;               // group g works on steps j = g (mod 2): buffer j & 1 = g
+    io.t_p = tmem_base + Cfg::kColP + g * 64 + lane_base;
+    io.m_pub = m_hand + g * 128 + r;
+    io.m_other = m_hand + (g ^ 1) * 128 + r;
+    io.hand_mine = hand + g * 4 + w;
+    io.hand_other = hand + (g ^ 1) * 4 + w;
     float m_mine = -INFINITY;  // offset this group's partial row sum refers to
     float l_run = 0.f;
-    int buf = g;               // j % 3
-    uint32_t s_par = 0;        // (j / 3) & 1
+    int slot2 = (g + 2) % STAGES;  // (j + 2) % STAGES: K ring slot of the step that inherits the score buffer
+    int j3 = g;                    // j % 3
+    uint32_t par3 = 0;             // (j / 3) & 1
+    int f3 = g;                    // (j - 2) % 3 and ((j - 2) / 3) & 1, valid from the group's second step
+    uint32_t fpar3 = 0;
     for (int j = g; j < n; j += 2) {
-      FRAY_CRIT_WAIT(s_full + buf, s_par, abort_flag, 0x201 + g, j);
+      FRAY_CRIT_WAIT(s_full + g, (j >> 1) & 1, abort_flag, 0x201 + g, j);
       tc_fence_after_sync();
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, g, j);
       const int kv0 = j * BN;
@@ -592,15 +430,34 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #ifdef FRAY_ATTN_TRACE
       if (trace_on && r == FRAY_TRACE_ROW && j < kTraceIters) tr = trace_sm + g * kTraceIters + j;
 #endif
-      softmax_step3<CTAS, FRAY_WS3_MODE>(tmem_base + buf * 128 + lane_base, pv_ready_addr + buf * 8, corr_ready + ((j - 1) & 3),
-                          alpha_buf + ((j - 1) & 3) * 128 + r, m_hand + g * 128 + r, m_hand + (g ^ 1) * 128 + r,
-                          hand + g * 4 + w, hand + (g ^ 1) * 4 + w, ((j - 1) >> 1) & 1, j == 0, need_mask, kv0, row,
-                          seq_k, causal, scale_log2, lane, m_mine, l_run, abort_flag, j, tr);
+      io.released_bar = (j + 2 < n) ? k_full_addr + slot2 * 8 : 0u;
+      io.pv_bar = pv_ready_addr + j3 * 8;
+      io.p_free_bar = (j >= 2) ? pv_done + f3 : nullptr;
+      io.p_free_parity = fpar3;
+      io.corr_bar = corr_ready + ((j - 1) & 3);
+      io.alpha_slot = alpha_buf + ((j - 1) & 3) * 128 + r;
+      io.hand_parity = ((j - 1) >> 1) & 1;
+      if (need_mask) {
+        softmax_step3<CTAS, FRAY_WS3_POLY, true>(io, j == 0, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run,
+                                                 abort_flag, j, tr);
+      } else {
+        softmax_step3<CTAS, FRAY_WS3_POLY, false>(io, j == 0, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run,
+                                                  abort_flag, j, tr);
+      }
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, g, j);
-      buf += 2;
-      if (buf >= 3) {
-        buf -= 3;
-        s_par ^= 1u;
+      slot2 += 2;
+      if (slot2 >= STAGES) slot2 -= STAGES;
+      if (j >= 2) {
+        f3 += 2;
+        if (f3 >= 3) {
+          f3 -= 3;
+          fpar3 ^= 1u;
+        }
+      }
+      j3 += 2;
+      if (j3 >= 3) {
+        j3 -= 3;
+        par3 ^= 1u;
       }
     }
     l_fin[g * 128 + r] = l_run;
@@ -614,16 +471,7 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_o = tmem_base + Cfg::kColO + lane_base;
     const uint32_t pv_ready_addr = leader_addr(pv_ready);
-    auto o_is_ready = [&](int buf) {
-      if (lane == 0) {
-        if constexpr (CTAS == 1) {
-          mbar_arrive(pv_ready + buf);
-        } else {
-          mbar_arrive_cluster(pv_ready_addr + buf * 8);
-        }
-      }
-    };
-    o_is_ready(0);  // step 0 overwrites O: nothing to rescale
+    if (lane == 0) arrive_leader(pv_ready_addr);  // step 0 overwrites O: nothing to rescale
     int buf = 1;                 // j % 3
     int pbuf = 0;                // (j - 1) % 3
     uint32_t ppar = 0;           // ((j - 1) / 3) & 1
@@ -647,7 +495,7 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tc_fence_before_sync();
       }
       __syncwarp();
-      o_is_ready(buf);
+      if (lane == 0) arrive_leader(pv_ready_addr + buf * 8);
       pbuf = buf;
       if (buf == 0) ppar ^= 1u;  // j just crossed a multiple of 3: so will j - 1 on the next turn
       if (++buf == 3) buf = 0;
@@ -754,22 +602,27 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const uint32_t t_o = tmem_base + Cfg::kColO;
       int slot = 0;
       uint32_t k_par = 0;
-      auto issue_qk = [&](int jj, int buf) __attribute__((always_inline)) {  // S(jj) = Q . K_jj^T into buffer jj % 3
+      auto issue_qk = [&](int jj) __attribute__((always_inline)) {  // S(jj) = Q . K_jj^T into buffer jj & 1
+        // K_jj has landed and the softmax group of step jj - 2 holds its scores in registers
         mbar_wait(k_full + slot, k_par, abort_flag, 0x501, jj);
         tc_fence_after_sync();
+#ifndef FRAY_TRACE_SM_DETAIL
         FRAY_TRACE(2, jj & 1, jj);
+#endif
         const uint32_t k_lo = kDescKLo | (((k_addr + slot * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
-        const uint32_t t_s = tmem_base + buf * 128;
+        const uint32_t t_s = tmem_base + (jj & 1) * 128;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
           const uint32_t koff = ((kk >> 2) * Cfg::kKPanelBytes + (kk & 3) * 32) >> 4;
           if (!(FRAY_WS3_SKIP & 1)) mma_ss_elect_g<CTAS>(t_s, q_lo + qoff, kDescKHi, k_lo + koff, kDescKHi, kIdescQK, kk > 0);
         }
-        mma_commit_elect_g<CTAS>(s_full + buf);
+        mma_commit_elect_g<CTAS>(s_full + (jj & 1));
         // the last ring entries are never refilled: no arrival may reach a CTA that has already left
         if (jj + STAGES < n) mma_commit_elect_g<CTAS>(k_empty + slot);
+#ifndef FRAY_TRACE_SM_DETAIL
         FRAY_TRACE(8, jj & 1, jj);
+#endif
         if (++slot == STAGES) {
           slot = 0;
           k_par ^= 1u;
@@ -778,25 +631,27 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       auto issue_pv = [&](int j, int buf, uint32_t par) __attribute__((always_inline)) {  // O (+)= P(j) . V_j
         FRAY_CRIT_WAIT(pv_ready + buf, par, abort_flag, 0x503, j);
         tc_fence_after_sync();
+#ifndef FRAY_TRACE_SM_DETAIL
         FRAY_TRACE(5, j & 1, j);
+#endif
         const uint32_t v_lo = kDescVLo | (((v_addr + buf * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
-        const uint32_t t_p = tmem_base + buf * 128;
+        const uint32_t t_p = tmem_base + Cfg::kColP + (j & 1) * 64;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
           if (!(FRAY_WS3_SKIP & 1)) mma_ts_elect_g<CTAS>(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
         mma_commit_elect_g<CTAS>(pv_done + buf);
+#ifndef FRAY_TRACE_SM_DETAIL
         FRAY_TRACE(7, j & 1, j);
+#endif
       };
 
       mbar_wait(q_full, 0, abort_flag, 0x511);
-      issue_qk(0, 0);
-      if (n > 1) issue_qk(1, 1);
+      issue_qk(0);
+      if (n > 1) issue_qk(1);
       int buf = 0;        // j % 3
       uint32_t par = 0;   // (j / 3) & 1
       for (int j = 0; j < n; ++j) {
-        int buf2 = buf + 2;
-        if (buf2 >= 3) buf2 -= 3;
-        if (j + 2 < n) issue_qk(j + 2, buf2);
+        if (j + 2 < n) issue_qk(j + 2);
         issue_pv(j, buf, par);
         if (++buf == 3) {
           buf = 0;
