@@ -42,7 +42,6 @@
 //
 // Every barrier wait is bounded (sm100_ptx.cuh).
 
-#include "fwd_ws_sm100.cuh"
 #include "host_sm100.cuh"
 #include "sm100_ptx.cuh"
 #include "softmax_tile_sm100.cuh"
@@ -51,7 +50,7 @@ namespace fray {
 namespace sm100 {
 
 template <int D, int STAGES, int CTAS>
-struct Ws3Cfg {
+struct AltCfg {
   static_assert(D == 64 || D == 128, "head dim must be 64 or 128");
   static_assert(CTAS == 1 || CTAS == 2, "one CTA or a pair");
   static_assert(CTAS == 1 || D == 128, "the paired kernel splits V into two 64-dim halves");
@@ -92,16 +91,9 @@ struct Ws3Cfg {
   static constexpr int kPvReadyCount = 8 * CTAS + 1;
 };
 
-#ifndef FRAY_WS3_X
-#define FRAY_WS3_X 0  // timing experiments: 1 no masking code, 2 no P-buffer check, 4 no fence at the release
-#endif
-#ifndef FRAY_WS3_SKIP
-#define FRAY_WS3_SKIP 0  // timing experiments only (wrong results): 1 no MMA instructions, 2 no K/V copies
-#endif
-
 // Share of the exponentials evaluated by polynomial on the FMA pipe (of every 4 pairs).
-#ifndef FRAY_WS3_POLY
-#define FRAY_WS3_POLY 1
+#ifndef FRAY_ALT_POLY
+#define FRAY_ALT_POLY 1
 #endif
 
 // Barriers and slots one softmax step touches (addresses are cluster-wide where the barrier lives in the
@@ -129,7 +121,7 @@ struct SoftmaxStepIo {
 // pipe needs for the tile's two products, so with every exponential on the unit the softmax can
 // never hide behind the tensor work.
 template <int CTAS, int POLY, bool MASK>
-__device__ __forceinline__ void softmax_step3(const SoftmaxStepIo& io, bool first_step, int kv0, int row,
+__device__ __forceinline__ void softmax_step_alt(const SoftmaxStepIo& io, bool first_step, int kv0, int row,
                                               int seq_k, int causal, float scale_log2, int lane, float& m_mine,
                                               float& l_run, volatile uint32_t* abort_flag, int step,
                                               unsigned int* tr = nullptr) {
@@ -189,12 +181,12 @@ __device__ __forceinline__ void softmax_step3(const SoftmaxStepIo& io, bool firs
   float m_prev = -INFINITY;
   if (!first_step) {
     // the other group decided the previous step's offset long ago
-    if (!(FRAY_WS3_X & 8)) mbar_wait(io.hand_other, io.hand_parity, abort_flag, 0x601, step);
+    mbar_wait(io.hand_other, io.hand_parity, abort_flag, 0x601, step);
     m_prev = *io.m_other;
   }
   // P.V(j - 2) was issued a whole step ago; that it has left the P buffer is tested here and only looked
   // at before the first store to the buffer
-  const bool p_free = (FRAY_WS3_X & 2) || io.p_free_bar == nullptr || mbar_test_wait(io.p_free_bar, io.p_free_parity);
+  const bool p_free = io.p_free_bar == nullptr || mbar_test_wait(io.p_free_bar, io.p_free_parity);
   const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
   FRAY_SM_TRACE(tr, 1);
   float m_j;
@@ -288,10 +280,10 @@ __device__ __forceinline__ void softmax_step3(const SoftmaxStepIo& io, bool firs
 
 template <int D, int STAGES, int CTAS>
 __global__ void __launch_bounds__(512, 1)
-attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+attn_fwd_alt_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, int num_heads,
                     int seq_len, int causal, float scale_log2, int kv_group, float* lse, int seq_k) {
-  using Cfg = Ws3Cfg<D, STAGES, CTAS>;
+  using Cfg = AltCfg<D, STAGES, CTAS>;
   constexpr int BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -438,10 +430,10 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       io.alpha_slot = alpha_buf + ((j - 1) & 3) * 128 + r;
       io.hand_parity = ((j - 1) >> 1) & 1;
       if (need_mask) {
-        softmax_step3<CTAS, FRAY_WS3_POLY, true>(io, j == 0, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run,
+        softmax_step_alt<CTAS, FRAY_ALT_POLY, true>(io, j == 0, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run,
                                                  abort_flag, j, tr);
       } else {
-        softmax_step3<CTAS, FRAY_WS3_POLY, false>(io, j == 0, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run,
+        softmax_step_alt<CTAS, FRAY_ALT_POLY, false>(io, j == 0, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run,
                                                   abort_flag, j, tr);
       }
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, g, j);
@@ -539,14 +531,10 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       for (int jj = 0; jj < n; ++jj) {
         mbar_wait(k_empty + slot, par ^ 1u, abort_flag, 0x401, jj);
         if (*abort_flag != 0) break;
-        if (FRAY_WS3_SKIP & 2) {
-          if (rank == 0) mbar_arrive(k_full + slot);
-        } else if (rank == 0) {
-          mbar_expect_tx(k_full + slot, CTAS * Cfg::kSlotBytes);
-        }
+        if (rank == 0) mbar_expect_tx(k_full + slot, CTAS * Cfg::kSlotBytes);
         uint8_t* dst = k_smem + slot * Cfg::kSlotBytes;
 #pragma unroll
-        for (int p = 0; p < ((FRAY_WS3_SKIP & 2) ? 0 : Cfg::kPanels); ++p) {
+        for (int p = 0; p < Cfg::kPanels; ++p) {
           if constexpr (CTAS == 1) {
             tma_load_4d(dst + p * Cfg::kKPanelBytes, &tm_k, k_full + slot, p * 64, jj * BN, h_kv, b);
           } else {
@@ -568,14 +556,10 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       for (int j = 0; j < n; ++j) {
         if (j >= 3) mbar_wait(pv_done + buf, par ^ 1u, abort_flag, 0x402, j);  // P.V(j - 3) has left the slot
         if (*abort_flag != 0) break;
-        if (FRAY_WS3_SKIP & 2) {
-          if (rank == 0) mbar_arrive(pv_ready + buf);
-        } else if (rank == 0) {
-          mbar_expect_tx(pv_ready + buf, CTAS * Cfg::kSlotBytes);
-        }
+        if (rank == 0) mbar_expect_tx(pv_ready + buf, CTAS * Cfg::kSlotBytes);
         uint8_t* dst = v_smem + buf * Cfg::kSlotBytes;
 #pragma unroll
-        for (int p = 0; p < ((FRAY_WS3_SKIP & 2) ? 0 : Cfg::kVPanels); ++p) {
+        for (int p = 0; p < Cfg::kVPanels; ++p) {
           if constexpr (CTAS == 1) {
             tma_load_4d(dst + p * Cfg::kVPanelBytes, &tm_v, pv_ready + buf, p * 64, j * BN, h_kv, b);
           } else {
@@ -615,7 +599,7 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t qoff = ((kk >> 2) * Cfg::kQPanelBytes + (kk & 3) * 32) >> 4;
           const uint32_t koff = ((kk >> 2) * Cfg::kKPanelBytes + (kk & 3) * 32) >> 4;
-          if (!(FRAY_WS3_SKIP & 1)) mma_ss_elect_g<CTAS>(t_s, q_lo + qoff, kDescKHi, k_lo + koff, kDescKHi, kIdescQK, kk > 0);
+          mma_ss_elect_g<CTAS>(t_s, q_lo + qoff, kDescKHi, k_lo + koff, kDescKHi, kIdescQK, kk > 0);
         }
         mma_commit_elect_g<CTAS>(s_full + (jj & 1));
         // the last ring entries are never refilled: no arrival may reach a CTA that has already left
@@ -638,7 +622,7 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const uint32_t t_p = tmem_base + Cfg::kColP + (j & 1) * 64;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          if (!(FRAY_WS3_SKIP & 1)) mma_ts_elect_g<CTAS>(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
+          mma_ts_elect_g<CTAS>(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
         mma_commit_elect_g<CTAS>(pv_done + buf);
 #ifndef FRAY_TRACE_SM_DETAIL
         FRAY_TRACE(7, j & 1, j);
@@ -675,10 +659,10 @@ attn_fwd_ws3_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
 // Host launcher.  Returns an AttnReturnCode.
 template <int D, int STAGES, int CTAS>
-inline int launch_attn_fwd_ws3(const operand_t* q, const operand_t* k, const operand_t* v, operand_t* o, const AttnShape& shp,
+inline int launch_attn_fwd_alt(const operand_t* q, const operand_t* k, const operand_t* v, operand_t* o, const AttnShape& shp,
                                const AttnStrides (&st)[4], const AttnExtras& ex, bool causal, float scale,
                                cudaStream_t stream) {
-  using Cfg = Ws3Cfg<D, STAGES, CTAS>;
+  using Cfg = AltCfg<D, STAGES, CTAS>;
   const AttnShape shp_kv{shp.B, shp.H / ex.kv_group, ex.seq_k, shp.D};
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   int rc = cached_attn_tensor_map(&tm_q, q, shp, st[0], Cfg::BM);
@@ -690,7 +674,7 @@ inline int launch_attn_fwd_ws3(const operand_t* q, const operand_t* k, const ope
   rc = cached_attn_tensor_map(&tm_o, o, shp, st[3], Cfg::BM);
   if (rc != kAttnOk) return rc;
 
-  auto kernel = attn_fwd_ws3_kernel<D, STAGES, CTAS>;
+  auto kernel = attn_fwd_alt_kernel<D, STAGES, CTAS>;
   rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes);
   if (rc != kAttnOk) return rc;
 

@@ -15,14 +15,14 @@ namespace fray {
 // Values written to `__return_code` by the launchers. 0 means the kernel was queued.
 enum AttnReturnCode : int {
   kAttnOk = 0,
-  kAttnBadShape = 1,        // batch/heads/seq_len not positive, or seq_len too large
+  kAttnBadShape = 1,        // a count is not positive, batch * heads exceeds 65535, K/V heads do not divide the
+                            // query heads, or the softmax scale is not positive and finite
   kAttnBadPointer = 2,      // null or not 16-byte aligned
   kAttnBadStride = 3,       // a stride is not a positive multiple of 8 elements (16 bytes)
   kAttnNoDriverEntry = 5,   // cuTensorMapEncodeTiled could not be resolved
   kAttnTensorMapFailed = 6, // the driver rejected the tensor map (layout not expressible)
   kAttnSmemAttrFailed = 7,  // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed
   kAttnLaunchFailed = 8,    // the launch itself reported an error
-  kAttnUnsupported = 9,     // this kernel kind does not implement grouped K/V heads or the LSE output
 };
 
 // Element strides of one [B,H,S,D] tensor; the D stride is 1 by contract.
@@ -45,15 +45,18 @@ struct AttnExtras {
   int seq_k;
 };
 
+// shp describes Q and O, shp_kv K and V (their own head count and length).  Strides of modes of
+// extent 1 are ignored.
 inline int validate_attn_args(const void* q, const void* k, const void* v, const void* o, const AttnShape& shp,
-                              const AttnStrides (&st)[4]) {
-  if (shp.B <= 0 || shp.H <= 0 || shp.S <= 0) return kAttnBadShape;
-  if (static_cast<int64_t>(shp.B) * shp.H > 0x7FFFFFFFLL / 2) return kAttnBadShape;
+                              const AttnShape& shp_kv, const AttnStrides (&st)[4]) {
+  if (shp.B <= 0 || shp.H <= 0 || shp.S <= 0 || shp_kv.H <= 0 || shp_kv.S <= 0) return kAttnBadShape;
+  if (static_cast<int64_t>(shp.B) * shp.H > 65535) return kAttnBadShape;  // batch * heads is a grid dimension
   const void* ptrs[4] = {q, k, v, o};
   for (int i = 0; i < 4; ++i) {
     if (ptrs[i] == nullptr || (reinterpret_cast<uintptr_t>(ptrs[i]) & 15u) != 0) return kAttnBadPointer;
+    const AttnShape& e = (i == 1 || i == 2) ? shp_kv : shp;
     const int64_t s3[3] = {st[i].b, st[i].h, st[i].s};
-    const int extent[3] = {shp.B, shp.H, shp.S};
+    const int extent[3] = {e.B, e.H, e.S};
     for (int d = 0; d < 3; ++d) {
       if (extent[d] > 1 && (s3[d] <= 0 || (s3[d] & 7) != 0)) return kAttnBadStride;
     }

@@ -34,17 +34,17 @@ namespace sm100 {
 // [2] = block y, [3] = extra. A non-zero [0] makes later CTAs return at entry.
 __device__ int fray_attn_status[4] = {0, 0, 0, 0};
 
-static constexpr long long kWaitLimitCycles = 400000000LL;  // ~0.2 s at 1.9 GHz
+// Cycle budget of one wait.  A translation unit may define FRAY_WAIT_LIMIT_CYCLES before including this
+// file (the wait-timeout test does, to make a wait run out in a millisecond).
+#ifndef FRAY_WAIT_LIMIT_CYCLES
+#define FRAY_WAIT_LIMIT_CYCLES 400000000LL  // ~0.2 s at 1.9 GHz
+#endif
+static constexpr long long kWaitLimitCycles = FRAY_WAIT_LIMIT_CYCLES;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ uint32_t lane_id() {
-  uint32_t l;
-  asm volatile("mov.u32 %0, %%laneid;" : "=r"(l));
-  return l;
-}
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -105,36 +105,6 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// Address forms: the barrier is named by its 32-bit shared-memory address.  A role that touches
-// many barriers keeps one base address and constant offsets instead of a 64-bit pointer each.
-__device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar_addr, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.b32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar_addr), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ void mbar_wait_a(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag,
-                                            uint32_t site, uint32_t extra = 0) {
-  if (mbar_try_wait_a(bar_addr, parity)) return;
-  const long long t0 = clock64();
-  uint32_t polls = 0;
-  while (!mbar_try_wait_a(bar_addr, parity)) {
-    if ((++polls & 31u) == 0u) {
-      if (*abort_flag) return;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        report_timeout(abort_flag, site, extra);
-        return;
-      }
-    }
-  }
-}
 
 // Same contract as mbar_wait, but polls with the non-blocking test_wait instead of the suspending
 // try_wait.  A suspended waiter was measured to resume a few hundred cycles after the barrier
@@ -242,7 +212,6 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void*
       : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
@@ -311,37 +280,6 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
       ".reg .pred p;\n"
       "setp.ne.b32 p, %4, 0;\n"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-      "}\n"
-      :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Warp-collective forms: the whole warp executes the call with uniform operands and one
-// elected lane issues the instruction.  Keeping the issuing code warp-uniform lets the
-// compiler hold descriptors in uniform registers, which makes back-to-back MMA issue several
-// times faster than issuing from a single-lane branch.  elect.sync picks the same lane for
-// the same member mask every time, so commits track the MMAs issued through these calls.
-__device__ __forceinline__ void mma_ss_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p, e;\n"
-      "elect.sync _|e, 0xffffffff;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
-      "}\n"
-      :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_elect(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p, e;\n"
-      "elect.sync _|e, 0xffffffff;\n"
-      "setp.ne.b32 p, %4, 0;\n"
-      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
       "}\n"
       :
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
@@ -456,15 +394,6 @@ __device__ __forceinline__ void mma_commit_elect_g(uint64_t* bar) {
   }
 }
 
-__device__ __forceinline__ void mma_commit_elect_a(uint32_t bar_addr) {
-  asm volatile(
-      "{\n"
-      ".reg .pred e;\n"
-      "elect.sync _|e, 0xffffffff;\n"
-      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
-      "}\n" ::"r"(bar_addr)
-      : "memory");
-}
 
 // Arrives once on `bar` when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
@@ -474,29 +403,8 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 
 // ---------------------------------------------------------------- TMEM load / store
 
-// Each lane of the warp reads 8 consecutive 32-bit columns of its own TMEM lane.
-__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr)
-               : "memory");
-}
 
-// Each lane of the warp writes 8 consecutive 32-bit columns of its own TMEM lane.
-__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
-               :
-               : "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr)
-               : "memory");
-}
 
-// Each lane of the warp reads 16 consecutive 32-bit columns of its own TMEM lane.
-__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr)
-               : "memory");
-}
 
 // Each lane of the warp writes 16 consecutive 32-bit columns of its own TMEM lane.
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -522,41 +430,13 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[
                : "memory");
 }
 
-// Each lane of the warp reads 64 consecutive 32-bit columns of its own TMEM lane.
-__device__ __forceinline__ void tmem_ld_x64(uint32_t taddr, uint32_t (&r)[64]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
-               : "r"(taddr)
-               : "memory");
-}
 
-// Each lane of the warp writes 64 consecutive 32-bit columns of its own TMEM lane.
-__device__ __forceinline__ void tmem_st_x64(uint32_t taddr, const uint32_t (&r)[64]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x64.b32 [%64], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63};"
-               :
-               : "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(r[32]), "r"(r[33]), "r"(r[34]), "r"(r[35]), "r"(r[36]), "r"(r[37]), "r"(r[38]), "r"(r[39]), "r"(r[40]), "r"(r[41]), "r"(r[42]), "r"(r[43]), "r"(r[44]), "r"(r[45]), "r"(r[46]), "r"(r[47]), "r"(r[48]), "r"(r[49]), "r"(r[50]), "r"(r[51]), "r"(r[52]), "r"(r[53]), "r"(r[54]), "r"(r[55]), "r"(r[56]), "r"(r[57]), "r"(r[58]), "r"(r[59]), "r"(r[60]), "r"(r[61]), "r"(r[62]), "r"(r[63]), "r"(taddr)
-               : "memory");
-}
 
 // ---------------------------------------------------------------- small math helpers
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-// Two base-2 exponentials in one special-function instruction: packed fp16 in, packed fp16 out.
-__device__ __forceinline__ uint32_t ex2_approx_f16x2(uint32_t x) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t add_f16x2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-__device__ __forceinline__ void unpack_half2(uint32_t v, float& lo, float& hi) {
-  asm("{\n.reg .f16 l, h;\nmov.b32 {l, h}, %2;\ncvt.f32.f16 %0, l;\ncvt.f32.f16 %1, h;\n}" : "=f"(lo), "=f"(hi) : "r"(v));
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float r;
@@ -594,10 +474,6 @@ __device__ __forceinline__ float ex2_poly(float x) {
   q = fmaf(q, f, 0.6932609677f);
   q = fmaf(q, f, 0.9999280572f);
   return __uint_as_float(__float_as_uint(q) + (__float_as_uint(t) << 23));
-}
-__device__ __forceinline__ void ex2_poly_pair(float x0, float x1, float& p0, float& p1) {
-  p0 = ex2_poly(x0);
-  p1 = ex2_poly(x1);
 }
 // 2^x for a packed pair on the FMA/ALU pipes: the same cubic as ex2_poly with the additions and the
 // Horner steps as packed f32x2 instructions (one issue slot per pair), the clamp and the exponent

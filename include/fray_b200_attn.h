@@ -30,14 +30,16 @@ extern "C" {
  *              num_heads and query head h reads K/V head h / (num_heads / num_kv_heads).
  *              seq_len counts the queries (rows of Q, O and Lse).  With causal != 0 query i
  *              sees keys 0..i whatever the two lengths are.
- * *_stride_*   in elements, positive multiples of 8 (ignored for modes of extent 1).
+ * *_stride_*   in elements, positive multiples of 8 (ignored for modes of extent 1 of that tensor).
+ * scale        positive and finite.  batch_size * num_heads is at most 65535.
  * Lse          null, or a 4-byte aligned device pointer to fp32 [batch, num_heads, seq]
  *              (contiguous) that receives log(sum_j exp(scale * q_i . k_j)) of every row.
  * stream       a cudaStream_t; the call returns once the kernel is queued.
  * __return_code receives 0 when the kernel was queued, otherwise (nothing launched):
- *              1 bad shape, 2 bad pointer, 3 bad stride, 5 driver entry point missing,
- *              6 tensor map rejected, 7 shared-memory attribute failed, 8 launch failed,
- *              9 this kernel kind supports neither num_kv_heads != num_heads nor Lse.
+ *              1 bad shape (a count not positive, batch * heads above 65535, num_kv_heads not a
+ *              divisor of num_heads, scale not positive and finite), 2 bad pointer, 3 bad stride,
+ *              5 driver entry point missing, 6 tensor map rejected, 7 shared-memory attribute
+ *              failed, 8 launch failed.
  */
 void launch(void* Q, void* K, void* V, void* O, int batch_size, int num_heads, int seq_len,
             int q_stride_b, int q_stride_h, int q_stride_s, int k_stride_b, int k_stride_h, int k_stride_s,
@@ -53,8 +55,9 @@ void launch(void* Q, void* K, void* V, void* O, int batch_size, int num_heads, i
  * (fray/jit_kernels/tuner.py:45-50 only sees the always-zero return code). */
 int fray_attn_status(int* out4, int clear);
 
-/* out4 = {kernel kind, head dim D, KV tile length, KV pipeline stages + 16 * polynomial-exp2
- * share} this library was instantiated with - the template keys the reference keeps only in the source text
+/* out4 = {kernel kind (0 single-role, 1 two query tiles per CTA, 2 one tile per CTA with two softmax
+ * groups on alternate KV steps, 3 the same on a CTA pair with 2-CTA MMA), head dim D, KV tile length,
+ * K/V pipeline stages} this library was instantiated with - the template keys the reference keeps only in the source text
  * (fray/jit_kernels/flashattn_cute.py:32-38). */
 void fray_attn_kernel_info(int* out4);
 

@@ -38,12 +38,13 @@ def test_every_library_exports_every_declared_symbol(built_kernels):
     assert len(seen) == len(built_kernels)  # one library per point of the space
 
 
-def _call(lib, q=0x1000, k=0x1000, v=0x1000, o=0x1000, B=1, H=1, S=128, strides=None, kv_heads=None, lse=0, Sk=None):
+def _call(lib, q=0x1000, k=0x1000, v=0x1000, o=0x1000, B=1, H=1, S=128, strides=None, kv_heads=None, lse=0, Sk=None,
+          scale=0.125):
     strides = strides or [8192, 8192, 64] * 4
     rc = ctypes.c_int(-1)
     lib.launch(ctypes.c_void_p(q), ctypes.c_void_p(k), ctypes.c_void_p(v), ctypes.c_void_p(o), B, H, S,
                *strides, H if kv_heads is None else kv_heads, S if Sk is None else Sk, ctypes.c_void_p(lse), ctypes.c_bool(False),
-               ctypes.c_float(0.125), ctypes.c_void_p(0), ctypes.byref(rc))
+               ctypes.c_float(scale), ctypes.c_void_p(0), ctypes.byref(rc))
     return rc.value
 
 
@@ -59,3 +60,15 @@ def test_launch_rejects_bad_arguments_without_touching_the_gpu(built_kernels):
     assert _call(lib, H=6, kv_heads=0) == 1
     assert _call(lib, Sk=0) == 1                # no keys
     assert _call(lib, lse=0x1002) == 2          # fp32 output not 4-byte aligned
+    assert _call(lib, scale=0.0) == 1 and _call(lib, scale=-1.0) == 1
+    assert _call(lib, scale=float("nan")) == 1 and _call(lib, scale=float("inf")) == 1
+    assert _call(lib, B=300, H=300) == 1        # batch * heads is a grid dimension: at most 65535
+    # strides are checked against each tensor's own extents: one query row over many keys still needs a
+    # legal K/V row stride
+    assert _call(lib, S=1, Sk=256, strides=[8192, 8192, 0] + [8192, 8192, 60] * 2 + [8192, 8192, 0]) == 3
+    import torch
+    if not torch.cuda.is_available():
+        # ... and strides of modes of extent 1 are ignored per tensor (one K/V head under six query heads).
+        # The call passes validation and stops where the driver is needed (code 5); with a GPU present it
+        # would go on to launch on the fake pointers, so this part only runs without one.
+        assert _call(lib, H=6, kv_heads=1, strides=[8192, 8192, 64, 8192, 0, 64, 8192, 0, 64, 8192, 8192, 64]) == 5

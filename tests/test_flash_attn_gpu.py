@@ -31,18 +31,35 @@ def all_variants():
     return [",".join(f"{k}={v}" for k, v in p) for p in sorted(pts)]
 
 
+def skip_unbuildable(variant, D):
+    """Points of one head dim's space forced on the other: the paired kernel is D = 128 only, and ring depths
+    are sized per head dim."""
+    keys = dict(kv.split("=") for kv in variant.split(",")) if variant != "tuned" else {}
+    if D == 64 and keys.get("KIND") == "3":
+        pytest.skip("the paired kernel (2-CTA MMA) is built for head dim 128")
+    if D == 128 and ((keys.get("KIND") == "1" and int(keys["STAGES"]) > 4) or (keys.get("KIND") == "2" and int(keys["STAGES"]) > 2)):
+        pytest.skip("ring depth of the D = 64 space: does not fit shared memory at D = 128")
+
+
+_current_variant = "tuned"
+
+
 @pytest.fixture(params=["tuned"] + all_variants())
 def variant(request, monkeypatch):
+    global _current_variant
     if request.param != "tuned":
         monkeypatch.setenv("FRAY_ATTN_FORCE", request.param)
     else:
         monkeypatch.delenv("FRAY_ATTN_FORCE", raising=False)
-    return request.param
+    _current_variant = request.param
+    yield request.param
+    _current_variant = "tuned"
 
 
 def run_op(q, k, v, causal=False, scale=None, out=None):
     """q,k,v: CUDA fp16 [B,H,S,D] (any supported strides). Returns the output tensor after a status check."""
     from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
+    skip_unbuildable(_current_variant, q.shape[-1])
     out = torch.zeros_like(q) if out is None else out
     flash_attn_cute(q, k, v, out, causal=causal, scale=scale)
     torch.cuda.synchronize()
@@ -87,33 +104,60 @@ def test_config2_readme_shape(variant):
     check(run_op(q, k, v), q, k, v, False)
 
 
-def test_config3_causal_sampled_units():
-    # Full size on the GPU; the oracle checks the first, a middle and the last (b,h) unit.
-    cfg = ref.CONFIGS[2]
-    units = [0, 61, 127]
-    (q, k, v), _ = config_tensors(2, units)
+_full_inputs = {}
+
+
+def _full_config_on_gpu(ci):
+    """All (b, h) units of a BASELINE configuration on the GPU, generated unit by unit from the seeds
+    (once per session: the variants of a test share them)."""
+    cfg = ref.CONFIGS[ci]
+    if ci not in _full_inputs:
+        _full_inputs.clear()             # one configuration at a time: up to 0.4 GB of host memory each
+        shape = (cfg["B"], cfg["H"], cfg["S"], cfg["D"])
+        _full_inputs[ci] = tuple(t.reshape(shape) for t in ref.make_inputs(ci))
+    return tuple(t.cuda() for t in _full_inputs[ci]), cfg
+
+
+def _check_units(out, q, k, v, units, H, causal):
+    """Compare the listed flat (b * H + h) units of a full-size result with the CPU oracle."""
+    for u in units:
+        b, h = divmod(u, H)
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        check(out[sl], q[sl], k[sl], v[sl], causal)
+
+
+def test_config3_full_grid_sampled_units(variant):
+    # The real launch: [4, 32, 4096, 128] causal, 128 units.  The oracle checks the first unit, one in the
+    # middle and the first, a middle and the last unit of the last batch.
+    if variant != "tuned" and "KIND=0" in variant:
+        pytest.skip("single-role kernel: covered at this size by the tuned choice's cross-check below")
+    (q, k, v), cfg = _full_config_on_gpu(2)
+    assert q.shape == (4, 32, 4096, 128)
     out = run_op(q, k, v, causal=True)
-    check(out, q, k, v, True)
+    _check_units(out, q, k, v, [0, 61, 96, 111, 127], cfg["H"], True)
 
 
-def test_config4_long_context_one_head():
-    (q, k, v), cfg = config_tensors(3, [7])
-    assert q.shape[2] == 16384
+def test_config4_full_grid_sampled_heads(variant):
+    # [1, 32, 16384, 128] causal: all 32 heads launched, three checked (the oracle needs ~1 GB per head)
+    if variant != "tuned" and "KIND=0" in variant:
+        pytest.skip("single-role kernel: see test_config3_full_grid_sampled_units")
+    (q, k, v), cfg = _full_config_on_gpu(3)
+    assert q.shape == (1, 32, 16384, 128)
     out = run_op(q, k, v, causal=True)
-    check(out, q, k, v, True)
+    _check_units(out, q, k, v, [0, 17, 31], cfg["H"], True)
 
 
-def test_config5_large_logits_and_transposed_q(variant):
-    cfg = ref.CONFIGS[4]
-    units = list(range(2 * cfg["H"]))               # two batches, all heads
-    q, k, v = ref.make_inputs(4, units)
-    B, H, S, D = 2, cfg["H"], cfg["S"], cfg["D"]
-    q, k, v = (t.reshape(B, H, S, D) for t in (q, k, v))
-    q_bshd = q.permute(0, 2, 1, 3).contiguous().cuda()      # storage [B,S,H,D]
+def test_config5_full_grid_large_logits_and_transposed_q(variant):
+    # [16, 16, 1024, 64], q passed as the transposed view of a [B, S, H, D] tensor: batch index > 1 with a
+    # strided q, all 256 units launched, units of the first, a middle and the last batch checked
+    (q, k, v), cfg = _full_config_on_gpu(4)
+    B, H, S, D = 16, cfg["H"], cfg["S"], cfg["D"]
+    assert q.shape == (B, H, S, D)
+    q_bshd = q.permute(0, 2, 1, 3).contiguous()             # storage [B,S,H,D]
     q_view = q_bshd.transpose(1, 2)                          # logical [B,H,S,D], non-contiguous
     assert not q_view.is_contiguous()
-    out = run_op(q_view, k.cuda(), v.cuda())
-    check(out, q, k, v, False)
+    out = run_op(q_view, k, v)
+    _check_units(out, q, k, v, [0, 5, 8 * H + 3, 15 * H, 15 * H + 15], H, False)
 
 
 # ---------------------------------------------------------------- edge cases
@@ -267,6 +311,32 @@ def test_host_buffer_call_matches_device_call(chunks, causal):
     assert torch.equal(hout, out.cpu())  # same kernel, same inputs: bit-identical
 
 
+@pytest.mark.parametrize("feature", ["bf16", "grouped_heads", "lse", "longer_keys"])
+def test_host_buffer_call_extensions(feature):
+    """Every extension of the device op is reachable from pinned host buffers too."""
+    from fray_b200.jit_kernels import flash_attn_cute, flash_attn_cute_host
+    torch.manual_seed(7)
+    dt = torch.bfloat16 if feature == "bf16" else torch.half
+    B, H, Hkv, Sq, Sk, D = 3, 4, (2 if feature == "grouped_heads" else 4), 256, (640 if feature == "longer_keys" else 256), 128
+    hq = torch.randn(B, H, Sq, D).to(dt).pin_memory()
+    hk, hv = (torch.randn(B, Hkv, Sk, D).to(dt).pin_memory() for _ in range(2))
+    hout = torch.zeros(B, H, Sq, D, dtype=dt).pin_memory()
+    hlse = torch.zeros(B, H, Sq).pin_memory() if feature == "lse" else None
+    flash_attn_cute_host(hq, hk, hv, hout, causal=True, lse=hlse, chunks=3)
+    torch.cuda.synchronize()
+    q, k, v = (t.cuda() for t in (hq, hk, hv))
+    out = torch.zeros_like(q)
+    lse = torch.zeros(B, H, Sq, device="cuda") if feature == "lse" else None
+    flash_attn_cute(q, k, v, out, causal=True, lse=lse)
+    torch.cuda.synchronize()
+    assert torch.equal(hout, out.cpu())
+    if lse is not None:
+        assert torch.equal(hlse, lse.cpu())
+    ke, ve = ref.expand_kv_heads(hk, hv, H)
+    if Sq == Sk:
+        check(hout, hq, ke, ve, True)
+
+
 @pytest.mark.gpu
 def test_host_buffer_call_rejects_pageable_and_device_tensors():
     from fray_b200.jit_kernels import flash_attn_cute_host
@@ -279,16 +349,9 @@ def test_host_buffer_call_rejects_pageable_and_device_tensors():
 
 
 # ---------------------------------------------------------------- grouped K/V heads and the LSE output
-# The persistent variant keeps the reference's feature set (return code 9 for either extension).
-def _skip_without_extras(variant):
-    if "KIND=2" in variant.split(","):
-        pytest.skip("the persistent variant implements neither grouped K/V heads nor the LSE output")
-
-
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("kv_heads", [1, 2, 8])
 def test_grouped_kv_heads(variant, kv_heads, causal):
-    _skip_without_extras(variant)
     g = torch.Generator().manual_seed(31 + kv_heads)
     B, H, S, D = 2, 8, 320, 128
     q = torch.randn(B, H, S, D, generator=g).half().cuda()
@@ -303,7 +366,7 @@ def test_grouped_kv_heads(variant, kv_heads, causal):
 @pytest.mark.parametrize("S,D", [(77, 64), (512, 128), (1500, 128)])
 def test_lse_output(variant, S, D, causal):
     from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
-    _skip_without_extras(variant)
+    skip_unbuildable(variant, D)
     g = torch.Generator().manual_seed(41)
     B, H = 2, 3
     q, k, v = (torch.randn(B, H, S, D, generator=g).half().cuda() for _ in range(3))
@@ -315,10 +378,8 @@ def test_lse_output(variant, S, D, causal):
     assert flash_attn_status()[0] == 0
     check(out, q, k, v, causal)
     want = ref.lse_fp32(q.cpu(), k.cpu(), causal)
-    # fp32 accumulation of approximate exponentials: absolute error of a natural logarithm.  The
-    # packed-fp16 exponential variant rounds every term to fp16 first (relative 5e-4 each).
-    tol = 3e-3 if "POLY=16" in variant.split(",") else 2e-4
-    assert (lse.cpu() - want).abs().max().item() <= tol
+    # fp32 accumulation of approximate exponentials: absolute error of a natural logarithm
+    assert (lse.cpu() - want).abs().max().item() <= 2e-4
     # the same call without lse gives the same attention output
     out2 = torch.zeros_like(q)
     flash_attn_cute(q, k, v, out2, causal=causal)
@@ -425,9 +486,9 @@ def test_bf16_operands(S, D, kv_heads, causal):
 @pytest.mark.parametrize("Sq,Sk", [(1, 700), (128, 1024), (300, 77), (513, 200), (64, 4096)])
 def test_query_and_key_lengths_differ(variant, Sq, Sk, causal):
     from fray_b200.jit_kernels import flash_attn_cute, flash_attn_status
-    _skip_without_extras(variant)
     g = torch.Generator().manual_seed(61)
     B, H, Hkv, D = 2, 4, 2, 128
+    skip_unbuildable(variant, D)
     q = torch.randn(B, H, Sq, D, generator=g).half().cuda()
     k, v = (torch.randn(B, Hkv, Sk, D, generator=g).half().cuda() for _ in range(2))
     out = torch.zeros_like(q)
@@ -444,5 +505,4 @@ def test_query_and_key_lengths_differ(variant, Sq, Sk, causal):
     want16 = torch.nn.functional.scaled_dot_product_attention(q.cpu(), ke, ve, is_causal=causal)
     assert (out.cpu().float() - want16.float()).abs().max().item() <= MAX_ABS
     assert ref.calc_diff(out.cpu(), want) <= MAX_DIFF
-    tol = 3e-3 if "POLY=16" in variant.split(",") else 2e-4   # see test_lse_output
-    assert (lse.cpu() - torch.logsumexp(s, -1)).abs().max().item() <= tol
+    assert (lse.cpu() - torch.logsumexp(s, -1)).abs().max().item() <= 2e-4

@@ -29,7 +29,7 @@ def test_arg_table_matches_template():
     assert names[-3:] == ["causal", "scale", "stream"]
     for n in names:
         assert n in op.template
-    for key in ("{KIND}", "{D}", "{BLOCK_N}", "{STAGES}", "{POLY}"):
+    for key in ("{KIND}", "{D}", "{BLOCK_N}", "{STAGES}"):
         assert key in op.template
 
 
@@ -43,9 +43,51 @@ def test_usable_strides():
 
 def test_forced_space(monkeypatch):
     monkeypatch.setenv("FRAY_ATTN_FORCE", "KIND=0, BLOCK_N=64, STAGES=1")
-    assert op.tuning_space(128) == ({"POLY": 0, "KIND": 0, "BLOCK_N": 64, "STAGES": 1},)
-    monkeypatch.setenv("FRAY_ATTN_FORCE", "KIND=1,BLOCK_N=128,STAGES=4,POLY=1")
-    assert op.tuning_space(128) == ({"POLY": 1, "KIND": 1, "BLOCK_N": 128, "STAGES": 4},)
+    assert op.tuning_space(128) == ({"KIND": 0, "BLOCK_N": 64, "STAGES": 1},)
+    monkeypatch.setenv("FRAY_ATTN_FORCE", "KIND=3,STAGES=6")
+    assert op.tuning_space(128) == ({"KIND": 3, "BLOCK_N": 128, "STAGES": 6},)
+    with pytest.raises(ValueError, match="head dim 128"):
+        op.tuning_space(64)              # the paired kernel splits V into two 64-dim halves
+
+
+def test_tuning_space_varies_tile_rows_stages_and_cta_pairing(monkeypatch):
+    monkeypatch.delenv("FRAY_ATTN_FORCE", raising=False)
+    for d in (64, 128):
+        space = op.tuning_space(d)
+        assert len({tuple(sorted(p.items())) for p in space}) == len(space)          # no duplicates
+        assert {p["KIND"] for p in space} >= {op.KIND_SIMPLE, op.KIND_TWO_TILES, op.KIND_ALTERNATING}
+        assert len({p["STAGES"] for p in space if p["KIND"] == op.KIND_TWO_TILES}) >= 2    # pipeline depth is searched
+        assert {p["BLOCK_N"] for p in space} == {64, 128}
+    assert op.KIND_PAIRED in {p["KIND"] for p in op.tuning_space(128)}               # 2-CTA MMA is a dimension at D = 128
+    assert op.KIND_PAIRED not in {p["KIND"] for p in op.tuning_space(64)}
+
+
+def test_prebuild_point_list_keeps_the_whole_space_when_a_point_is_forced(monkeypatch):
+    monkeypatch.delenv("FRAY_ATTN_FORCE", raising=False)
+    whole = op._space_points((64, 128), forced=False)
+    monkeypatch.setenv("FRAY_ATTN_FORCE", "KIND=0,BLOCK_N=64,STAGES=1")
+    assert op._space_points((64, 128), forced=False) == whole        # pruning keeps these
+    assert len(op._space_points((64, 128), forced=True)) == 4        # 2 head dims x fp16/bf16
+    assert op.os.environ["FRAY_ATTN_FORCE"] == "KIND=0,BLOCK_N=64,STAGES=1"
+
+
+def test_status_of_a_process_that_launched_nothing():
+    assert op.flash_attn_status() == (0, 0, 0, 0)
+
+
+def test_fast_path_cache_is_bounded(monkeypatch):
+    monkeypatch.setattr(op, "_fast_path", op.OrderedDict())
+    for i in range(3 * op._FAST_PATH_ENTRIES):
+        op._fast_path[i] = i
+        while len(op._fast_path) > op._FAST_PATH_ENTRIES:
+            op._fast_path.popitem(last=False)
+    assert len(op._fast_path) == op._FAST_PATH_ENTRIES and (3 * op._FAST_PATH_ENTRIES - 1) in op._fast_path
+
+
+def test_host_entry_refuses_pageable_and_mismatched_operands():
+    t = torch.zeros(1, 2, 128, 64, dtype=torch.half)
+    with pytest.raises(AssertionError, match="pinned"):
+        op.flash_attn_cute_host(t, t, t, t.clone())
 
 
 class FakeRuntime:
