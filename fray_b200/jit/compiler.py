@@ -130,7 +130,10 @@ def get_nvcc_flags() -> Tuple[str, ...]:
     return (
         "-std=c++17", "-O3", "--expt-relaxed-constexpr", "--expt-extended-lambda", "-lineinfo",
         _ARCH_FLAG, "-shared", ptxas, "--diag-suppress=177,174,940",
-        "--compiler-options=-fPIC,-O3,-Wno-deprecated-declarations,-Wno-abi", *extra,
+        # -fno-gnu-unique: function-local statics of inline functions and templates (per-device bookkeeping in
+        # the launchers) must stay private to each built library; as GNU unique symbols they would be shared
+        # by every library the process loads, whatever the dlopen flags
+        "--compiler-options=-fPIC,-O3,-Wno-deprecated-declarations,-Wno-abi,-fno-gnu-unique", *extra,
     )
 
 
