@@ -11,7 +11,7 @@
 //
 //   warps 0-3   softmax group 0: KV steps 0, 2, 4, ... of the tile (thread r owns row r)
 //   warps 4-7   softmax group 1: KV steps 1, 3, 5, ... of the same rows
-//   warps 8-11  correction group: rescales O when the exponent offset moved; epilogue
+//   warps 8-11  statistics group: row max and exponent offset of every step, O rescale when it moved; epilogue
 //   warp 12     MMA issue (leader CTA only when paired)
 //   warp 13     TMA producer for Q and the K ring (STAGES slots)
 //   warp 14     TMA producer for V (three slots)
@@ -34,11 +34,15 @@
 // P.V(j) on the one that collects the softmax warps that stored P(j), the correction warps that made
 // O ready, and the bytes of V_j.
 //
-// The two groups share the row state through shared memory: the group of step j reads the offset
-// m(j-1) the other group published, decides m(j) (lazily: it moves only when the row max grew by
-// more than 2^8 in the scaled domain), publishes it together with the factor for O, and keeps the
-// partial row sum of its own steps (rescaled when the offset moved since its last step).  The
-// correction group adds the two partial sums at the end.
+// The row statistics are not the softmax groups' job: the statistics group scans S(j) for the row max as
+// soon as the scores are complete, decides the step's exponent offset m(j) (lazily: it moves only when
+// the row max grew by more than 2^8 in the scaled domain; the sequence lives in that group's registers,
+// so nothing is exchanged between the softmax groups), rescales O when the offset moved and publishes
+// m(j).  A softmax thread waits for m(j) only (which implies S(j)), pulls its row into registers, and
+// spends its step on the exponentials; it keeps the partial row sum of its own steps (rescaled when the
+// offset moved since its last step) and the statistics group adds the two partial sums at the end.  The
+// max scan and the exponentials of a step thus run in different warps of the same schedulers, which
+// gives the in-order issue three streams to interleave instead of two.
 //
 // Every barrier wait is bounded (sm100_ptx.cuh).
 
@@ -70,12 +74,12 @@ struct AltCfg {
   static constexpr int kOffK = kQTileBytes;
   static constexpr int kOffV = kOffK + STAGES * kSlotBytes;
   static constexpr int kOffBars = kOffV + 3 * kSlotBytes;
-  static constexpr int kNumBars = 1 + 2 * STAGES + 2 + 3 + 3 + 4 + 8 + 1;
+  static constexpr int kNumBars = 1 + 2 * STAGES + 2 + 3 + 3 + 2 + 8 + 1;
   static constexpr int kOffStats = ((kOffBars + kNumBars * 8 + 16 + 127) / 128) * 128;
-  static constexpr int kStatsBytes = (4 + 2 + 2 + 2) * 128 * 4;  // alpha[4], m_hand[2], l_fin[2], m_fin[2] x 128 rows
+  static constexpr int kStatsBytes = (2 + 2 + 2) * 128 * 4;  // m_slot[2], l_fin[2], m_fin[2] x 128 rows
 #ifdef FRAY_ATTN_TRACE
   static constexpr int kOffTrace = kOffStats + kStatsBytes;
-  static constexpr int kSmemBytes = kOffTrace + 4 * 800 + 1024;
+  static constexpr int kSmemBytes = kOffTrace + 4 * 960 + 1024;
 #else
   static constexpr int kSmemBytes = kOffStats + kStatsBytes + 1024;  // + alignment slack
 #endif
@@ -84,9 +88,9 @@ struct AltCfg {
   static constexpr uint32_t kColP = 256, kColO = 384;
   static constexpr int kRegsSoftmax = 184, kRegsCorrection = 80, kRegsOther = 64;
   // arrivals on a "S(j) may start" barrier: the leader's K producer (with the byte count of both CTAs'
-  // copies) and the softmax warps of every CTA that released the score buffer (step j - 2)
-  static constexpr int kKFullCount = 4 * CTAS + 1;
-  // arrivals on a "P.V(j) may start" barrier: softmax and correction warps of every CTA, and the
+  // copies) and the softmax and statistics warps of every CTA that are done with the score buffer (step j - 2)
+  static constexpr int kKFullCount = 8 * CTAS + 1;
+  // arrivals on a "P.V(j) may start" barrier: softmax and statistics warps of every CTA, and the
   // leader's V producer (with the byte count of both CTAs' copies)
   static constexpr int kPvReadyCount = 8 * CTAS + 1;
 };
@@ -105,111 +109,61 @@ struct SoftmaxStepIo {
   uint32_t pv_bar;         // told that P(j) is stored
   uint64_t* p_free_bar;    // P.V(j - 2) complete: its P buffer may be overwritten (null on a group's first step)
   uint32_t p_free_parity;
-  uint64_t* corr_bar;      // factor for O published (not on a row's first step)
-  float* alpha_slot;
-  float* m_pub;            // this group's published offset of the row
-  const float* m_other;    // the other group's
-  uint64_t* hand_mine;     // barriers (one arrival per warp) behind those two slots
-  uint64_t* hand_other;
-  uint32_t hand_parity;
+  uint64_t* m_bar;         // the statistics warp of these rows has published m(j) (which implies S(j) complete)
+  uint32_t m_parity;
+  const float* m_slot;     // ... here
 };
 
-// One softmax step of one thread (= one query row).  The 128 scores are pulled into registers in one
-// go and the score buffer is released right away; the rest works from registers.
+// Masks the scores of keys past the end of the sequence or above the causal diagonal.
+template <int N>
+__device__ __forceinline__ void mask_scores(uint32_t (&h)[N], int kv_first, int row, int seq_k, int causal) {
+#pragma unroll
+  for (int c = 0; c < N; ++c) {
+    const int kv = kv_first + c;
+    if (kv >= seq_k || (causal && kv > row)) h[c] = __float_as_uint(-INFINITY);
+  }
+}
+
+// One softmax step of one thread (= one query row): exp2(S*c - m(j)*c) for the row's 128 scores, rounded
+// to 16 bit into P(j), and the row sum of the unrounded values.  The scores are pulled into registers in
+// one go and the score buffer is released right away; the rest works from registers.
 // POLY of every 4 pairs of exponentials are evaluated by polynomial on the FMA pipe: a 128 x 128 tile
 // needs the special-function unit (16 results per clock and SM) for exactly as long as the tensor
 // pipe needs for the tile's two products, so with every exponential on the unit the softmax can
 // never hide behind the tensor work.
 template <int CTAS, int POLY, bool MASK>
-__device__ __forceinline__ void softmax_step_alt(const SoftmaxStepIo& io, bool first_step, int kv0, int row,
-                                              int seq_k, int causal, float scale_log2, int lane, float& m_mine,
-                                              float& l_run, volatile uint32_t* abort_flag, int step,
-                                              unsigned int* tr = nullptr) {
+__device__ __forceinline__ void softmax_step_alt(const SoftmaxStepIo& io, int kv0, int row, int seq_k, int causal,
+                                                 float scale_log2, int lane, float& m_mine, float& l_run,
+                                                 volatile uint32_t* abort_flag, int step, unsigned int* tr = nullptr) {
   static_assert(POLY >= 0 && POLY <= 2, "0, 1 or 2 of every 4 pairs by polynomial");
-  auto load_half = [&](uint32_t (&h)[64], int half) {
-    tmem_ld_x32(io.t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(h[0]));
-    tmem_ld_x32(io.t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(h[32]));
-  };
-  auto mask_half = [&](uint32_t (&h)[64], int half) {
-#pragma unroll
-    for (int c = 0; c < 64; ++c) {
-      const int kv = kv0 + half * 64 + c;
-      if (kv >= seq_k || (causal && kv > row)) h[c] = __float_as_uint(-INFINITY);
-    }
-  };
-  float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-  auto max_half = [&](const uint32_t (&h)[64]) {
-#pragma unroll
-    for (int c = 0; c < 64; c += 8) {
-      mx0 = max3(mx0, __uint_as_float(h[c + 0]), __uint_as_float(h[c + 4]));
-      mx1 = max3(mx1, __uint_as_float(h[c + 1]), __uint_as_float(h[c + 5]));
-      mx2 = max3(mx2, __uint_as_float(h[c + 2]), __uint_as_float(h[c + 6]));
-      mx3 = max3(mx3, __uint_as_float(h[c + 3]), __uint_as_float(h[c + 7]));
-    }
-  };
-
+  FRAY_CRIT_WAIT(io.m_bar, io.m_parity, abort_flag, 0x201, step);
+  const float m_j = *io.m_slot;
+  tc_fence_after_sync();
+  FRAY_SM_TRACE(tr, 0);
   uint32_t sa[64], sb[64];
-  load_half(sa, 0);
-  load_half(sb, 1);
-#ifdef FRAY_TRACE_SM_DETAIL
-  FRAY_SM_TRACE(tr, 8);
-#endif
+  tmem_ld_x32(io.t_s, reinterpret_cast<uint32_t(&)[32]>(sa[0]));
+  tmem_ld_x32(io.t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sa[32]));
+  tmem_ld_x32(io.t_s + 64, reinterpret_cast<uint32_t(&)[32]>(sb[0]));
+  tmem_ld_x32(io.t_s + 96, reinterpret_cast<uint32_t(&)[32]>(sb[32]));
   tmem_wait_ld();
-#ifdef FRAY_TRACE_SM_DETAIL
-  FRAY_SM_TRACE(tr, 5);
-#endif
   tc_fence_before_sync();
   __syncwarp();
-  if (lane == 0 && io.released_bar != 0) {  // S(j + 2) may overwrite the scores now
+  if (lane == 0 && io.released_bar != 0) {  // this warp's part of "S(j + 2) may overwrite the scores"
     if constexpr (CTAS == 1) {
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(io.released_bar) : "memory");
     } else {
       mbar_arrive_cluster(io.released_bar);
     }
   }
-#ifdef FRAY_TRACE_SM_DETAIL
-  FRAY_SM_TRACE(tr, 7);
-#endif
-  if constexpr (MASK) {
-    mask_half(sa, 0);
-    mask_half(sb, 1);
-  }
-  max_half(sa);
-  max_half(sb);
+  FRAY_SM_TRACE(tr, 1);
   // Barrier tests behind the loads, not beside them: a wait issued while tensor-memory loads are in
   // flight queues behind them (measured ~150 cycles per satisfied wait).
-  float m_prev = -INFINITY;
-  if (!first_step) {
-    // the other group decided the previous step's offset long ago
-    mbar_wait(io.hand_other, io.hand_parity, abort_flag, 0x601, step);
-    m_prev = *io.m_other;
-  }
   // P.V(j - 2) was issued a whole step ago; that it has left the P buffer is tested here and only looked
-  // at before the first store to the buffer
+  // at before the first store to the buffer.
   const bool p_free = io.p_free_bar == nullptr || mbar_test_wait(io.p_free_bar, io.p_free_parity);
-  const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-  FRAY_SM_TRACE(tr, 1);
-  float m_j;
-  if (first_step) {
-    m_j = mx;
-    *io.m_pub = m_j;
-    __syncwarp();
-    if (lane == 0) mbar_arrive(io.hand_mine);
-  } else {
-    const float m_new = fmaxf(mx, m_prev);
-    float alpha = 1.f;
-    m_j = m_prev;
-    if ((m_new - m_prev) * scale_log2 > kRescaleThreshold) {
-      alpha = ex2_approx((m_prev - m_new) * scale_log2);
-      m_j = m_new;
-    }
-    *io.m_pub = m_j;
-    *io.alpha_slot = alpha;
-    __syncwarp();
-    if (lane == 0) {
-      mbar_arrive(io.hand_mine);
-      mbar_arrive(io.corr_bar);
-    }
+  if constexpr (MASK) {
+    mask_scores(sa, kv0, row, seq_k, causal);
+    mask_scores(sb, kv0 + 64, row, seq_k, causal);
   }
   if (m_j != m_mine) {
     // the offset moved since this group's last step: bring its partial row sum along
@@ -295,17 +249,16 @@ attn_fwd_alt_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   uint64_t* q_full = bars;                // [1]       producer(s) -> MMA
   uint64_t* k_full = q_full + 1;          // [STAGES]  K producer(s) + softmax -> MMA: S(j) may start (slot j % STAGES)
   uint64_t* k_empty = k_full + STAGES;    // [STAGES]  MMA -> K producer
-  uint64_t* s_full = k_empty + STAGES;    // [2]       MMA -> softmax: S(j) complete in buffer j & 1
-  uint64_t* pv_ready = s_full + 2;        // [3]       softmax + correction + V producer -> MMA: P.V(j) may start (j % 3)
-  uint64_t* pv_done = pv_ready + 3;       // [3]       MMA -> correction, V producer, softmax: P.V(j) complete (j % 3)
-  uint64_t* corr_ready = pv_done + 3;     // [4]       softmax -> correction: factor of step j >= 1 in slot (j - 1) & 3
-  uint64_t* hand = corr_ready + 4;        // [2][4]    softmax group g, warp w -> same warp of the other group
-  uint64_t* fin = hand + 8;               // [1]       softmax -> correction: partial row sums published
+  uint64_t* s_full = k_empty + STAGES;    // [2]       MMA -> statistics: S(j) complete in buffer j & 1
+  uint64_t* pv_ready = s_full + 2;        // [3]       softmax + statistics + V producer -> MMA: P.V(j) may start (j % 3)
+  uint64_t* pv_done = pv_ready + 3;       // [3]       MMA -> statistics, V producer: P.V(j) complete (j % 3)
+  uint64_t* p_free = pv_done + 3;         // [2]       MMA -> softmax: P.V(j) complete, its P buffer (j & 1) may be overwritten
+  uint64_t* m_ready = p_free + 2;         // [2][4]    statistics warp w -> softmax warp w of group j & 1: m(j) published
+  uint64_t* fin = m_ready + 8;            // [1]       softmax -> statistics: partial row sums published
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
-  float* alpha_buf = reinterpret_cast<float*>(smem + Cfg::kOffStats);  // [4][128]
-  float* m_hand = alpha_buf + 4 * 128;                                 // [2][128]
-  float* l_fin = m_hand + 2 * 128;                                     // [2][128]
+  float* m_slot = reinterpret_cast<float*>(smem + Cfg::kOffStats);     // [2][128]  m(j) of the row, slot j & 1
+  float* l_fin = m_slot + 2 * 128;                                     // [2][128]
   float* m_fin = l_fin + 2 * 128;                                      // [2][128]
 #ifdef FRAY_ATTN_TRACE
   unsigned int* trace_sm = reinterpret_cast<unsigned int*>(smem + Cfg::kOffTrace);
@@ -347,8 +300,8 @@ attn_fwd_alt_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_init(pv_ready + i, Cfg::kPvReadyCount);
       mbar_init(pv_done + i, 1);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(corr_ready + i, 4);
-    for (int i = 0; i < 8; ++i) mbar_init(hand + i, 1);
+    for (int i = 0; i < 2; ++i) mbar_init(p_free + i, 1);
+    for (int i = 0; i < 8; ++i) mbar_init(m_ready + i, 1);
     mbar_init(fin, 8);
     fence_barrier_init();
     prefetch_tensormap(&tm_q);
@@ -396,26 +349,18 @@ attn_fwd_alt_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const uint32_t lane_base = static_cast<uint32_t>(w * 32) << 16;
     const uint32_t k_full_addr = leader_addr(k_full);
     const uint32_t pv_ready_addr = leader_addr(pv_ready);
-    // both score buffers start out free: the arrivals S(0) and S(1) wait for besides their K tiles
+    // both score buffers start out free: this warp's share of the arrivals S(0) and S(1) wait for
     if (lane == 0 && g < n) arrive_leader(k_full_addr + g * 8);
     SoftmaxStepIo io;
     io.t_s = tmem_base + g * 128 + lane_base;               // group g works on steps j = g (mod 2): buffer j & 1 = g
     io.t_p = tmem_base + Cfg::kColP + g * 64 + lane_base;
-    io.m_pub = m_hand + g * 128 + r;
-    io.m_other = m_hand + (g ^ 1) * 128 + r;
-    io.hand_mine = hand + g * 4 + w;
-    io.hand_other = hand + (g ^ 1) * 4 + w;
+    io.m_bar = m_ready + g * 4 + w;
+    io.m_slot = m_slot + g * 128 + r;
     float m_mine = -INFINITY;  // offset this group's partial row sum refers to
     float l_run = 0.f;
     int slot2 = (g + 2) % STAGES;  // (j + 2) % STAGES: K ring slot of the step that inherits the score buffer
     int j3 = g;                    // j % 3
-    uint32_t par3 = 0;             // (j / 3) & 1
-    int f3 = g;                    // (j - 2) % 3 and ((j - 2) / 3) & 1, valid from the group's second step
-    uint32_t fpar3 = 0;
     for (int j = g; j < n; j += 2) {
-      FRAY_CRIT_WAIT(s_full + g, (j >> 1) & 1, abort_flag, 0x201 + g, j);
-      tc_fence_after_sync();
-      if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, g, j);
       const int kv0 = j * BN;
       const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0));
       unsigned int* tr = nullptr;
@@ -424,53 +369,101 @@ attn_fwd_alt_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #endif
       io.released_bar = (j + 2 < n) ? k_full_addr + slot2 * 8 : 0u;
       io.pv_bar = pv_ready_addr + j3 * 8;
-      io.p_free_bar = (j >= 2) ? pv_done + f3 : nullptr;
-      io.p_free_parity = fpar3;
-      io.corr_bar = corr_ready + ((j - 1) & 3);
-      io.alpha_slot = alpha_buf + ((j - 1) & 3) * 128 + r;
-      io.hand_parity = ((j - 1) >> 1) & 1;
+      io.p_free_bar = (j >= 2) ? p_free + g : nullptr;   // P.V(j - 2) is the buffer's ((j - 2) / 2)-th tenant
+      io.p_free_parity = ((j - 2) >> 1) & 1;
+      io.m_parity = (j >> 1) & 1;
       if (need_mask) {
-        softmax_step_alt<CTAS, FRAY_ALT_POLY, true>(io, j == 0, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run,
-                                                 abort_flag, j, tr);
+        softmax_step_alt<CTAS, FRAY_ALT_POLY, true>(io, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run, abort_flag, j, tr);
       } else {
-        softmax_step_alt<CTAS, FRAY_ALT_POLY, false>(io, j == 0, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run,
-                                                  abort_flag, j, tr);
+        softmax_step_alt<CTAS, FRAY_ALT_POLY, false>(io, kv0, row, seq_k, causal, scale_log2, lane, m_mine, l_run, abort_flag, j, tr);
       }
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, g, j);
       slot2 += 2;
       if (slot2 >= STAGES) slot2 -= STAGES;
-      if (j >= 2) {
-        f3 += 2;
-        if (f3 >= 3) {
-          f3 -= 3;
-          fpar3 ^= 1u;
-        }
-      }
       j3 += 2;
-      if (j3 >= 3) {
-        j3 -= 3;
-        par3 ^= 1u;
-      }
+      if (j3 >= 3) j3 -= 3;
     }
     l_fin[g * 128 + r] = l_run;
     m_fin[g * 128 + r] = m_mine;
     __syncwarp();
     if (lane == 0) mbar_arrive(fin);
   } else if (warp < 12) {
-    // =============================================================== correction group + epilogue
+    // =============================================================== statistics group + epilogue
     set_max_regs_dec<Cfg::kRegsCorrection>();
     const int r = tid & 127;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int w = warp & 3;
+    const int row = m0 + r;
+    const uint32_t lane_base = static_cast<uint32_t>(w * 32) << 16;
     const uint32_t t_o = tmem_base + Cfg::kColO + lane_base;
+    const uint32_t k_full_addr = leader_addr(k_full);
     const uint32_t pv_ready_addr = leader_addr(pv_ready);
-    if (lane == 0) arrive_leader(pv_ready_addr);  // step 0 overwrites O: nothing to rescale
-    int buf = 1;                 // j % 3
-    int pbuf = 0;                // (j - 1) % 3
-    uint32_t ppar = 0;           // ((j - 1) / 3) & 1
-    for (int j = 1; j < n; ++j) {
-      const int k = (j - 1) & 3;  // step 0 publishes no factor: step j is the slot's ((j - 1) / 4)-th use
-      mbar_wait(corr_ready + k, ((j - 1) >> 2) & 1, abort_flag, 0x301, j);
-      const float alpha = alpha_buf[k * 128 + r];
+    // both score buffers start out free: this warp's share of the arrivals S(0) and S(1) wait for
+    if (lane == 0) {
+      arrive_leader(k_full_addr);
+      if (n > 1) arrive_leader(k_full_addr + 8);
+    }
+    float m_run = -INFINITY;     // m(j - 1)
+    int buf = 0;                 // j % 3
+    int pbuf = 2;                // (j - 1) % 3 and ((j - 1) / 3) & 1 (from j = 1)
+    uint32_t ppar = 1;
+    int slot2 = 2 % STAGES;      // (j + 2) % STAGES
+    for (int j = 0; j < n; ++j) {
+      const int g = j & 1;
+      mbar_wait(s_full + g, (j >> 1) & 1, abort_flag, 0x301, j);
+      tc_fence_after_sync();
+      if (r == FRAY_TRACE_ROW) FRAY_TRACE(10, g, j);
+      // row max of S(j), 32 columns at a time, the next load under the current chunk's arithmetic
+      const int kv0 = j * BN;
+      const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0));
+      const uint32_t t_s = tmem_base + g * 128 + lane_base;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      auto max_chunk = [&](uint32_t (&h)[32], int c0) {
+        if (need_mask) mask_scores(h, kv0 + c0, row, seq_k, causal);
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          mx0 = max3(mx0, __uint_as_float(h[c + 0]), __uint_as_float(h[c + 4]));
+          mx1 = max3(mx1, __uint_as_float(h[c + 1]), __uint_as_float(h[c + 5]));
+          mx2 = max3(mx2, __uint_as_float(h[c + 2]), __uint_as_float(h[c + 6]));
+          mx3 = max3(mx3, __uint_as_float(h[c + 3]), __uint_as_float(h[c + 7]));
+        }
+      };
+      {
+        uint32_t ha[32], hb[32];
+        tmem_ld_x32(t_s, ha);
+        tmem_wait_ld();
+        tmem_ld_x32(t_s + 32, hb);
+        max_chunk(ha, 0);
+        tmem_wait_ld();
+        tmem_ld_x32(t_s + 64, ha);
+        max_chunk(hb, 32);
+        tmem_wait_ld();
+        tmem_ld_x32(t_s + 96, hb);
+        max_chunk(ha, 64);
+        tmem_wait_ld();
+        // this warp's part of "S(j + 2) may overwrite the scores"
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0 && j + 2 < n) arrive_leader(k_full_addr + slot2 * 8);
+        max_chunk(hb, 96);
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // the step's offset: the row max on a row's first step, afterwards moved only when the max outgrew it
+      float alpha = 1.f;
+      float m_j = m_run;
+      if (j == 0) {
+        m_j = mx;
+      } else {
+        const float m_new = fmaxf(mx, m_run);
+        if ((m_new - m_run) * scale_log2 > kRescaleThreshold) {
+          alpha = ex2_approx((m_run - m_new) * scale_log2);
+          m_j = m_new;
+        }
+      }
+      m_run = m_j;
+      m_slot[g * 128 + r] = m_j;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(m_ready + g * 4 + w);
+      if (r == FRAY_TRACE_ROW) FRAY_TRACE(11, g, j);
       if (__any_sync(0xffffffffu, alpha != 1.f)) {
         mbar_wait(pv_done + pbuf, ppar, abort_flag, 0x311, j);  // P.V(j - 1) complete
         tc_fence_after_sync();
@@ -485,18 +478,20 @@ attn_fwd_alt_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
         tmem_wait_st();
         tc_fence_before_sync();
+        __syncwarp();
       }
-      __syncwarp();
-      if (lane == 0) arrive_leader(pv_ready_addr + buf * 8);
+      if (lane == 0) arrive_leader(pv_ready_addr + buf * 8);  // O is ready for P.V(j)
       pbuf = buf;
       if (buf == 0) ppar ^= 1u;  // j just crossed a multiple of 3: so will j - 1 on the next turn
       if (++buf == 3) buf = 0;
+      slot2 += 1;
+      if (slot2 >= STAGES) slot2 -= STAGES;
     }
     // Epilogue: the two groups' partial row sums, each relative to the offset of that group's last
     // step, are brought to the final offset (offsets never decrease) and added.
     mbar_wait(fin, 0, abort_flag, 0x321, n);
     const float m_a = m_fin[r], m_b = m_fin[128 + r];
-    const float m_f = fmaxf(m_a, m_b);
+    const float m_f = m_run;
     float l = 0.f;
     if (m_a != -INFINITY) l += l_fin[r] * ex2_approx((m_a - m_f) * scale_log2);
     if (m_b != -INFINITY) l += l_fin[128 + r] * ex2_approx((m_b - m_f) * scale_log2);
@@ -584,15 +579,9 @@ attn_fwd_alt_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const uint32_t k_addr = smem_u32(k_smem);
       const uint32_t v_addr = smem_u32(v_smem);
       const uint32_t t_o = tmem_base + Cfg::kColO;
-      int slot = 0;
-      uint32_t k_par = 0;
-      auto issue_qk = [&](int jj) __attribute__((always_inline)) {  // S(jj) = Q . K_jj^T into buffer jj & 1
-        // K_jj has landed and the softmax group of step jj - 2 holds its scores in registers
-        mbar_wait(k_full + slot, k_par, abort_flag, 0x501, jj);
+      auto issue_qk = [&](int jj, int slot) __attribute__((always_inline)) {  // S(jj) = Q . K_jj^T into buffer jj & 1
         tc_fence_after_sync();
-#ifndef FRAY_TRACE_SM_DETAIL
         FRAY_TRACE(2, jj & 1, jj);
-#endif
         const uint32_t k_lo = kDescKLo | (((k_addr + slot * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
         const uint32_t t_s = tmem_base + (jj & 1) * 128;
 #pragma unroll
@@ -604,42 +593,45 @@ attn_fwd_alt_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         mma_commit_elect_g<CTAS>(s_full + (jj & 1));
         // the last ring entries are never refilled: no arrival may reach a CTA that has already left
         if (jj + STAGES < n) mma_commit_elect_g<CTAS>(k_empty + slot);
-#ifndef FRAY_TRACE_SM_DETAIL
         FRAY_TRACE(8, jj & 1, jj);
-#endif
-        if (++slot == STAGES) {
-          slot = 0;
-          k_par ^= 1u;
-        }
       };
-      auto issue_pv = [&](int j, int buf, uint32_t par) __attribute__((always_inline)) {  // O (+)= P(j) . V_j
-        FRAY_CRIT_WAIT(pv_ready + buf, par, abort_flag, 0x503, j);
+      auto issue_pv = [&](int j, int buf) __attribute__((always_inline)) {  // O (+)= P(j) . V_j
         tc_fence_after_sync();
-#ifndef FRAY_TRACE_SM_DETAIL
         FRAY_TRACE(5, j & 1, j);
-#endif
         const uint32_t v_lo = kDescVLo | (((v_addr + buf * Cfg::kSlotBytes) & 0x3FFFF) >> 4);
         const uint32_t t_p = tmem_base + Cfg::kColP + (j & 1) * 64;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
           mma_ts_elect_g<CTAS>(t_o, t_p + kk * 8, v_lo + ((kk * 2048) >> 4), kDescVHi, kIdescPV, (j > 0 || kk > 0));
         mma_commit_elect_g<CTAS>(pv_done + buf);
-#ifndef FRAY_TRACE_SM_DETAIL
+        mma_commit_elect_g<CTAS>(p_free + (j & 1));
         FRAY_TRACE(7, j & 1, j);
-#endif
       };
 
+      // Fixed order S(0) S(1) | S(2) PV(0) | S(3) PV(1) ...  (Issuing whichever product's barrier is ready
+      // first was tried: polling two barriers without suspending took issue slots from the softmax warps
+      // of the same scheduler and the suspending form reacts hundreds of cycles late; both measured slower.)
       mbar_wait(q_full, 0, abort_flag, 0x511);
-      issue_qk(0);
-      if (n > 1) issue_qk(1);
-      int buf = 0;        // j % 3
-      uint32_t par = 0;   // (j / 3) & 1
-      for (int j = 0; j < n; ++j) {
-        if (j + 2 < n) issue_qk(j + 2);
-        issue_pv(j, buf, par);
+      int slot = 0, buf = 0;           // jq % STAGES, jp % 3
+      uint32_t k_par = 0, pv_par = 0;  // parities of the barriers those wait on
+      auto next_qk = [&](int jq) __attribute__((always_inline)) {
+        // K_jq has landed and both readers of S(jq - 2) hold what they need of it
+        mbar_wait(k_full + slot, k_par, abort_flag, 0x501, jq);
+        issue_qk(jq, slot);
+        if (++slot == STAGES) {
+          slot = 0;
+          k_par ^= 1u;
+        }
+      };
+      next_qk(0);
+      if (n > 1) next_qk(1);
+      for (int jp = 0; jp < n; ++jp) {
+        if (jp + 2 < n) next_qk(jp + 2);
+        FRAY_CRIT_WAIT(pv_ready + buf, pv_par, abort_flag, 0x503, jp);
+        issue_pv(jp, buf);
         if (++buf == 3) {
           buf = 0;
-          par ^= 1u;
+          pv_par ^= 1u;
         }
       }
     }

@@ -61,7 +61,7 @@ struct WsCfg {
   static constexpr int kOffStats = kOffBars + ((kNumBars * 8 + 16 + 127) / 128) * 128;  // alpha[2][128]
 #ifdef FRAY_ATTN_TRACE
   static constexpr int kOffTrace = kOffStats + 2 * 128 * 4;
-  static constexpr int kSmemBytes = kOffTrace + 4 * 800 + 1024;
+  static constexpr int kSmemBytes = kOffTrace + 4 * 960 + 1024;
 #else
   static constexpr int kSmemBytes = kOffStats + 2 * 128 * 4 + 1024;  // + alignment slack
 #endif

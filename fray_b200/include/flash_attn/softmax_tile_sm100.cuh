@@ -39,7 +39,7 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 #define FRAY_TRACE_ROW 0  // which row's thread stamps the softmax events
 #endif
 #ifdef FRAY_ATTN_TRACE
-static constexpr int kTraceEvents = 10, kTraceIters = 40;
+static constexpr int kTraceEvents = 12, kTraceIters = 40;
 static constexpr int kTraceWords = kTraceEvents * 2 * kTraceIters;
 __device__ unsigned int fray_attn_trace_buf[kTraceWords];
 #define FRAY_TRACE(event, tile, iter)                                                              \

@@ -60,16 +60,27 @@ class JITTuner:
     # ------------------------------------------------------------------ timing
     @staticmethod
     def time_candidate(runtime: Runtime, args: tuple, launches: int = 20) -> float:
-        """Milliseconds for ``launches`` back-to-back calls after an L2 flush (reference: tuner.py:52-63)."""
-        start = torch.cuda.Event(enable_timing=True)
-        end = torch.cuda.Event(enable_timing=True)
-        torch.empty(int(256e6 // 4), dtype=torch.int, device="cuda").zero_()
-        start.record()
-        for _ in range(launches):
+        """Milliseconds for ``launches`` back-to-back calls after an L2 flush (reference: tuner.py:52-63).
+
+        Differences from the reference: three untimed launches first (the first launch of a library pays
+        module loading and the tensor-map encodings), and the better of two timed rounds, so that a
+        candidate is not dropped for one slow round on a shared machine.
+        """
+        for _ in range(3):
             assert runtime(*args) == 0
-        end.record()
-        end.synchronize()
-        return start.elapsed_time(end)
+        best = None
+        for _ in range(2):
+            start = torch.cuda.Event(enable_timing=True)
+            end = torch.cuda.Event(enable_timing=True)
+            torch.empty(int(256e6 // 4), dtype=torch.int, device="cuda").zero_()
+            start.record()
+            for _ in range(launches):
+                assert runtime(*args) == 0
+            end.record()
+            end.synchronize()
+            elapsed = start.elapsed_time(end)
+            best = elapsed if best is None else min(best, elapsed)
+        return best
 
     # ------------------------------------------------------------------ main entry
     def compile_and_tune(self, name: str, keys: Dict[str, Any], space: tuple, includes: tuple, arg_defs: tuple,
