@@ -317,18 +317,15 @@ def main():
     from fray_b200.jit_kernels import flash_attn_cute, flash_attn_cute_host, flash_attn_status
     from fray_b200.jit_kernels.tuner import jit_tuner
     from fray_b200.multi_gpu import shard_units
-    # This rank's (b,h) units.  Synthetic N(0,1) inputs, one device generator seed per unit, so a unit holds
-    # the same data whichever rank owns it.
+    # This rank's (b,h) units.  Synthetic N(0,1) inputs: every rank draws the whole workload from the same
+    # seed (three launches) and keeps its block, so a unit holds the same data whichever rank owns it.
     n_units = B * H
     strong = world > 1 and args.scaling == "strong"
     lo, hi = shard_units(n_units, rank, world) if strong else (0, n_units)
     n_local = hi - lo
-    q, k, v = (torch.empty(n_local, S, D, device="cuda", dtype=torch.half) for _ in range(3))
-    gen = torch.Generator(device="cuda")
-    for u in range(n_local):
-        gen.manual_seed(42 * 1000 + lo + u)
-        for t in (q, k, v):
-            t[u] = torch.randn(S, D, generator=gen, device="cuda", dtype=torch.float32).half()
+    gen = torch.Generator(device="cuda").manual_seed(42 * 1000)
+    q, k, v = (torch.randn(n_units, S, D, generator=gen, device="cuda", dtype=torch.float32)[lo:hi].half().contiguous()
+               for _ in range(3))
     out = torch.zeros_like(q)
     # the op sees [B, H, S, D] on one GPU (the reference's call), [1, units, S, D] for a shard
     shape4 = (B, H, S, D) if not strong else (1, n_local, S, D)

@@ -86,7 +86,13 @@ struct AltCfg {
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB shared memory of one CTA");
   static constexpr int kTmemCols = 512;
   static constexpr uint32_t kColP = 256, kColO = 384;
-  static constexpr int kRegsSoftmax = 184, kRegsCorrection = 80, kRegsOther = 64;
+#ifndef FRAY_ALT_REGS_STATS
+#define FRAY_ALT_REGS_STATS 112
+#endif
+  // register budgets after setmaxnreg (softmax, statistics, MMA/producer warps): their sum over the 16
+  // warps is the CTA's allocation of 512 x 128 registers
+  static constexpr int kRegsSoftmax = 184, kRegsCorrection = FRAY_ALT_REGS_STATS, kRegsOther = 144 - FRAY_ALT_REGS_STATS;
+  static_assert(256 * kRegsSoftmax + 128 * kRegsCorrection + 128 * kRegsOther <= 512 * 128, "register budgets exceed the CTA's allocation");
   // arrivals on a "S(j) may start" barrier: the leader's K producer (with the byte count of both CTAs'
   // copies) and the softmax and statistics warps of every CTA that are done with the score buffer (step j - 2)
   static constexpr int kKFullCount = 8 * CTAS + 1;
