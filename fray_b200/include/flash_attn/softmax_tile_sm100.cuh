@@ -26,9 +26,9 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// Waits on the critical path (scores ready, probabilities ready) use the suspending form: polling
+// Waits on the critical path (scores ready, probabilities ready) use the plain suspending form: polling
 // reacted no faster in measurements and executed ~30 % more instructions, which costs clock under the
-// power cap.
+// power cap, and try_wait with a short suspend-time hint (10 or 30 ns) measured 1 % slower.
 #define FRAY_CRIT_WAIT mbar_wait
 
 // Optional role timeline for bring-up and tuning: with -DFRAY_ATTN_TRACE one thread per role of
@@ -68,27 +68,29 @@ inline int read_attn_trace(unsigned int* out, int max_words) {
 static constexpr float kRescaleThreshold = 8.0f;
 
 // t_s        tensor-memory address of this thread's lane at column 0 of the S tile (P overwrites it)
-// p_bar      four consecutive mbarriers, arrival count 4 (one per warp of the group): chunk q of P stored
+// p_bar      PCHUNKS consecutive mbarriers, arrival count 4 (one per warp of the group): chunk q of P stored
 // corr_bar   mbarrier (count 4) telling the correction group that alpha_slot holds this step's factor
 // alpha_slot where this row's rescale factor is published (skipped on the first tile of a row)
 // first_tile no running state yet: the tile max becomes the offset, nothing is published
-// need_mask  some key of the tile is past seq_len or above the causal diagonal
+// MASK       some key of the tile is past seq_len or above the causal diagonal (two instantiations: the
+//            masking code costs the unmasked steps several per cent even when it is branched around)
 // The whole row is pulled into registers at once, the row max uses three-input max instructions, the
 // scaling and the row sum packed f32x2 arithmetic (one issue slot per pair).  Every exponential goes
 // to the special-function unit: a share by polynomial on the FMA pipe was measured slower here (the
 // chain softmax -> P.V -> next S bounds this kernel, not the unit).
-template <int BN>
+template <int BN, int PCHUNKS, bool MASK>
 __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
-                                                bool first_tile, bool need_mask, int kv0, int row, int seq_len, int causal,
+                                                bool first_tile, int kv0, int row, int seq_len, int causal,
                                                 float scale_log2, int lane, float& m_ref, float& l_run) {
   static_assert(BN == 128, "written for 128-key tiles");
+  static_assert(PCHUNKS == 4 || PCHUNKS == 2, "P is handed over in 4 chunks of 32 keys or 2 of 64");
   uint32_t sa[64], sb[64];
   tmem_ld_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sa[0]));
   tmem_ld_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sa[32]));
   tmem_ld_x32(t_s + 64, reinterpret_cast<uint32_t(&)[32]>(sb[0]));
   tmem_ld_x32(t_s + 96, reinterpret_cast<uint32_t(&)[32]>(sb[32]));
   tmem_wait_ld();
-  if (need_mask) {
+  if constexpr (MASK) {
 #pragma unroll
     for (int c = 0; c < 64; ++c) {
       const int kv = kv0 + c;
@@ -121,11 +123,14 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
   const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
   uint64_t rsp0 = 0ull, rsp1 = 0ull;
   const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(neg_m, neg_m);
-  // 32 keys: exponentials, row sum from the unrounded values, 16-bit rounding, store as chunk q, hand-over
-  auto chunk = [&](const uint32_t (&h)[64], int off, int q) {
-    uint32_t pk[16];
+  // One chunk of KEYS keys: exponentials, row sum from the unrounded values, 16-bit rounding, store as
+  // chunk q of P.  The hand-over of a chunk (wait for the store, fence, arrive) is issued after the NEXT
+  // chunk's arithmetic: the store's latency then hides under that arithmetic, and only the last chunk's
+  // wait sits in the step.
+  constexpr int KEYS = BN / PCHUNKS;
+  auto compute = [&](const uint32_t (&h)[64], int off, uint32_t (&pk)[KEYS / 2]) {
 #pragma unroll
-    for (int c = 0; c < 32; c += 8) {
+    for (int c = 0; c < KEYS; c += 8) {
       uint64_t p[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -143,16 +148,42 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
         pk[(c >> 1) + e] = pack_half2(p0, p1);
       }
     }
-    tmem_st_x16(t_s + q * 16, pk);
+  };
+  auto store = [&](const uint32_t (&pk)[KEYS / 2], int q) {
+    if constexpr (KEYS == 32) {
+      tmem_st_x16(t_s + q * 16, pk);
+    } else {
+      tmem_st_x32(t_s + q * 32, pk);
+    }
+  };
+  auto hand_over = [&](int q) {  // every store issued so far has landed: chunk q may be consumed
     tmem_wait_st();
     tc_fence_before_sync();
     __syncwarp();
     if (lane == 0) mbar_arrive(p_bar + q);
   };
-  chunk(sa, 0, 0);
-  chunk(sa, 32, 1);
-  chunk(sb, 0, 2);
-  chunk(sb, 32, 3);
+  uint32_t pa[KEYS / 2], pb[KEYS / 2];
+  if constexpr (PCHUNKS == 4) {
+    compute(sa, 0, pa);
+    store(pa, 0);
+    compute(sa, 32, pb);
+    hand_over(0);
+    store(pb, 1);
+    compute(sb, 0, pa);
+    hand_over(1);
+    store(pa, 2);
+    compute(sb, 32, pb);
+    hand_over(2);
+    store(pb, 3);
+    hand_over(3);
+  } else {
+    compute(sa, 0, pa);
+    store(pa, 0);
+    compute(sb, 0, pb);
+    hand_over(0);
+    store(pb, 1);
+    hand_over(1);
+  }
   float r0, r1, r2, r3;
   unpack_f32x2(rsp0, r0, r1);
   unpack_f32x2(rsp1, r2, r3);
