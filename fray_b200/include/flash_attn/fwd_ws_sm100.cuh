@@ -18,8 +18,9 @@
 // Issue order in the MMA warp: S0(0) S1(0) | PV0(0) S0(1) PV1(0) S1(1) | PV0(1) S0(2) ...
 // so that while group 0 runs the softmax of S0(j+1) the tensor cores work on PV1(j) and
 // S1(j+1), and vice versa.  (One issuing warp per tile and turn-taking of the softmax groups on
-// the special-function unit were both measured slower than this fixed alternation.)  P.V is issued in four key chunks as the
-// softmax hands them over, so only the last quarter of it sits behind the softmax.
+// the special-function unit were both measured slower than this fixed alternation.)  P.V is
+// issued in two key chunks as the softmax hands them over, so only the second half of it sits
+// behind the softmax.
 //
 // Online softmax in base 2 with lazy rescaling: a tile's exponent offset m_ref only moves
 // when the running max grew by more than 2^8 in the scaled domain; until then P may exceed
