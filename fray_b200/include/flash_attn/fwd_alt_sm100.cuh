@@ -673,7 +673,8 @@ inline int launch_attn_fwd_alt(const operand_t* q, const operand_t* k, const ope
   if (rc != kAttnOk) return rc;
 
   auto kernel = attn_fwd_alt_kernel<D, STAGES, CTAS>;
-  rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes);
+  rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes, Cfg::kThreads,
+                                256 * Cfg::kRegsSoftmax + 128 * Cfg::kRegsCorrection + 128 * Cfg::kRegsOther);
   if (rc != kAttnOk) return rc;
 
   const int tiles = (shp.S + Cfg::BM - 1) / Cfg::BM;

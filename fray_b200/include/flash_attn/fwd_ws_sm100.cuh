@@ -133,6 +133,7 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
   if (tid == 0) {
     FRAY_TRACE(6, 0, 0);  // CTA entry
+    FRAY_TRACE_NS(6, 0, 10);
     *abort_flag = (*reinterpret_cast<volatile int*>(&fray_attn_status[0]) != 0) ? 2u : 0u;
     for (int i = 0; i < 2; ++i) {
       mbar_init(q_full + i, 1);
@@ -181,12 +182,17 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(0, i, j);
       const int kv0 = j * BN;
       const bool need_mask = (kv0 + BN > seq_k) || (causal && (kv0 + BN - 1 > m0 + i * Cfg::BM));
+#ifdef FRAY_ATTN_TRACE
+      unsigned int* tr = (trace_on && r == FRAY_TRACE_ROW && j < kTraceIters) ? trace_sm + i * kTraceIters + j : nullptr;
+#else
+      unsigned int* tr = nullptr;
+#endif
       if (need_mask) {
         softmax_tile<BN, Cfg::kPChunks, true>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, kv0, row, seq_k,
-                                              causal, scale_log2, lane, m_ref, l_run);
+                                              causal, scale_log2, lane, m_ref, l_run, tr);
       } else {
         softmax_tile<BN, Cfg::kPChunks, false>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, kv0, row, seq_k,
-                                               causal, scale_log2, lane, m_ref, l_run);
+                                               causal, scale_log2, lane, m_ref, l_run, tr);
       }
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);
     }
@@ -352,7 +358,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 #ifdef FRAY_ATTN_TRACE
-  if (tid == 0) FRAY_TRACE(6, 0, 2);  // CTA exit
+  if (tid == 0) {
+    FRAY_TRACE(6, 0, 2);  // CTA exit
+    FRAY_TRACE_NS(6, 0, 11);
+  }
   __syncthreads();
   if (trace_on)
     for (int w = tid; w < kTraceWords; w += Cfg::kThreads) fray_attn_trace_buf[w] = trace_sm[w];
@@ -377,7 +386,7 @@ inline int launch_attn_fwd_ws(const operand_t* q, const operand_t* k, const oper
   if (rc != kAttnOk) return rc;
 
   auto kernel = attn_fwd_ws_kernel<D, BN, STAGES>;
-  rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes);
+  rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes, Cfg::kThreads, 256 * Cfg::kRegsSoftmax + 128 * Cfg::kRegsCorrection + 128 * Cfg::kRegsOther);
   if (rc != kAttnOk) return rc;
   dim3 grid((shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM), shp.B * shp.H);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,

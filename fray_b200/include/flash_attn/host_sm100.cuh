@@ -144,8 +144,12 @@ inline int cached_attn_tensor_map(CUtensorMap* map, const void* base, const Attn
 // attributes are per device; the reference sets the attribute on every launch,
 // fray/include/flash_attn/flashattn_cute.cuh:231).  Tag makes the bookkeeping unique per kernel
 // configuration: kernels of equal signature share a function-pointer type.
+// regs_after_setmaxnreg: for kernels whose warps re-balance registers with setmaxnreg, the sum of
+// the budgets over all threads.  setmaxnreg.inc draws from the CTA's allocation at launch (threads x
+// registers per thread as compiled) and blocks without bound if that pool cannot cover it, so a
+// kernel compiled with fewer registers than its budgets assume is refused here instead.
 template <class Tag, class Kernel>
-inline int ensure_dynamic_smem(Kernel kernel, int bytes) {
+inline int ensure_dynamic_smem(Kernel kernel, int bytes, int threads = 0, int regs_after_setmaxnreg = 0) {
   constexpr int kMaxDevices = 64;
   static bool done[kMaxDevices] = {};
   int dev = -1;
@@ -155,6 +159,14 @@ inline int ensure_dynamic_smem(Kernel kernel, int bytes) {
   }
   const bool tracked = dev >= 0 && dev < kMaxDevices;
   if (tracked && done[dev]) return kAttnOk;
+  if (regs_after_setmaxnreg > 0) {
+    cudaFuncAttributes attr;
+    if (cudaFuncGetAttributes(&attr, kernel) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return kAttnLaunchFailed;
+    }
+    if (attr.numRegs * threads < regs_after_setmaxnreg) return kAttnLaunchFailed;
+  }
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
     (void)cudaGetLastError();
     return kAttnSmemAttrFailed;

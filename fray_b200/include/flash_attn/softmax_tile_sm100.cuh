@@ -47,6 +47,16 @@ __device__ unsigned int fray_attn_trace_buf[kTraceWords];
     if (trace_on && (iter) < kTraceIters)                                                          \
       trace_sm[((event) * 2 + (tile)) * kTraceIters + (iter)] = static_cast<unsigned int>(clock64()); \
   } while (0)
+// Wall-clock stamp (nanoseconds, low 32 bits) beside a cycle stamp: the two together give the SM clock the
+// kernel really ran at.
+#define FRAY_TRACE_NS(event, tile, iter)                                                           \
+  do {                                                                                             \
+    if (trace_on) {                                                                                \
+      unsigned long long ns_;                                                                      \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns_));                                      \
+      trace_sm[((event) * 2 + (tile)) * kTraceIters + (iter)] = static_cast<unsigned int>(ns_);    \
+    }                                                                                              \
+  } while (0)
 inline int read_attn_trace(unsigned int* out, int max_words) {
   const int n = max_words < kTraceWords ? max_words : kTraceWords;
   if (cudaMemcpyFromSymbol(out, fray_attn_trace_buf, sizeof(unsigned int) * n) != cudaSuccess) return -1;
@@ -54,6 +64,7 @@ inline int read_attn_trace(unsigned int* out, int max_words) {
 }
 #else
 #define FRAY_TRACE(event, tile, iter) do { } while (0)
+#define FRAY_TRACE_NS(event, tile, iter) do { } while (0)
 #endif
 
 // Timeline stamps inside the softmax step (compiled in with -DFRAY_ATTN_TRACE only): `tr` points at
@@ -81,7 +92,8 @@ static constexpr float kRescaleThreshold = 8.0f;
 template <int BN, int PCHUNKS, bool MASK>
 __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
                                                 bool first_tile, int kv0, int row, int seq_len, int causal,
-                                                float scale_log2, int lane, float& m_ref, float& l_run) {
+                                                float scale_log2, int lane, float& m_ref, float& l_run,
+                                                unsigned int* tr = nullptr) {
   static_assert(BN == 128, "written for 128-key tiles");
   static_assert(PCHUNKS == 4 || PCHUNKS == 2, "P is handed over in 4 chunks of 32 keys or 2 of 64");
   uint32_t sa[64], sb[64];
@@ -90,6 +102,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
   tmem_ld_x32(t_s + 64, reinterpret_cast<uint32_t(&)[32]>(sb[0]));
   tmem_ld_x32(t_s + 96, reinterpret_cast<uint32_t(&)[32]>(sb[32]));
   tmem_wait_ld();
+  FRAY_SM_TRACE(tr, 1);
   if constexpr (MASK) {
 #pragma unroll
     for (int c = 0; c < 64; ++c) {
@@ -120,6 +133,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
     __syncwarp();
     if (lane == 0) mbar_arrive(corr_bar);
   }
+  FRAY_SM_TRACE(tr, 2);
   const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
   uint64_t rsp0 = 0ull, rsp1 = 0ull;
   const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(neg_m, neg_m);
@@ -178,10 +192,14 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
     hand_over(3);
   } else {
     compute(sa, 0, pa);
+    FRAY_SM_TRACE(tr, 3);
     store(pa, 0);
     compute(sb, 0, pb);
+    FRAY_SM_TRACE(tr, 9);
     hand_over(0);
+    FRAY_SM_TRACE(tr, 10);
     store(pb, 1);
+    FRAY_SM_TRACE(tr, 11);
     hand_over(1);
   }
   float r0, r1, r2, r3;
