@@ -78,7 +78,7 @@ class ClockSampler:
     def __init__(self, gpu_index: int, period_s: float = 0.002):
         self.gpu_index = gpu_index
         self.period_s = period_s
-        self.samples = []       # (sm_mhz, reasons bitmask)
+        self.samples = []       # (sm_mhz, reasons bitmask, board power in W)
         self.sm_max = None
         self._stop = threading.Event()
         self.thread = None
@@ -108,7 +108,11 @@ class ClockSampler:
             try:
                 clk = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
                 why = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
-                self.samples.append((float(clk), int(why)))
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                except Exception:
+                    watts = None
+                self.samples.append((float(clk), int(why), watts))
             except Exception as exc:
                 self.error = repr(exc)
                 return
@@ -128,10 +132,13 @@ class ClockSampler:
             "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap,
         }
         seen = 0
-        for _, why in self.samples:
+        for _, why, _ in self.samples:
             seen |= why
         reasons = sorted(n for n, bit in names.items() if seen & bit)
-        return {"sm_mhz": statistics.median(c for c, _ in self.samples), "sm_max_mhz": self.sm_max,
+        clocks = [c for c, _, _ in self.samples]
+        watts = [w for _, _, w in self.samples if w is not None]
+        return {"sm_mhz": statistics.median(clocks), "sm_min_mhz": min(clocks), "sm_max_mhz": self.sm_max,
+                "power_w": statistics.median(watts) if watts else None,
                 "reasons": reasons, "samples": len(self.samples)}
 
 
@@ -224,16 +231,20 @@ def run_library_bar(args, B, H, S, D, causal):
         for _ in range(max(args.warmup, 3)):
             step()
         torch.cuda.synchronize()
+        sampler = ClockSampler(torch.cuda.current_device())
+        sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
             step()
         e1.record()
         torch.cuda.synchronize()
+        clocks = sampler.stop()
         ms = e0.elapsed_time(e1) / args.steps
         line = {"impl": args.impl, "metric": "flash_attn_fwd_tflops", "value": flops_of(B, H, S, D, causal) / ms / 1e9,
                 "unit": "TFLOP/s", "ms_per_step": ms, "steps": args.steps, "warmup": args.warmup,
-                "config": workload_config(args, B, H, S, D, causal, 1), "note": "library kernel, comparison bar only"}
+                "config": workload_config(args, B, H, S, D, causal, 1), "clocks": clocks,
+                "note": "library kernel, comparison bar only"}
     except Exception as exc:  # backend not available for this shape / build
         line = {"impl": args.impl, "unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
     print(json.dumps(line), flush=True)
@@ -281,7 +292,7 @@ def verify_shard(out_local, q, k, v, lo, H, causal, dist, n_units, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "sdpa-flash", "sdpa-cudnn", "flash-attn"])
     ap.add_argument("--workload", default="headline", choices=sorted(WORKLOADS))
