@@ -8,6 +8,7 @@
 #include "host_sm100.cuh"
 #include "fwd_ws_sm100.cuh"
 #include "fwd_alt_sm100.cuh"
+#include "fwd_one_sm100.cuh"
 
 namespace fray {
 
@@ -18,6 +19,8 @@ enum AttnKernelKind : int {
   kAttnAlternating = 2,        // one 128-row tile per CTA, scores and probabilities in separate tensor-memory buffers,
                              // two softmax groups on alternate KV steps
   kAttnPaired = 3,           // the same on a pair of CTAs (cta_group::2): 256 rows per pair, half of K and V per CTA
+  kAttnOneTile = 4,          // one 128-row tile per CTA, producer / MMA / softmax roles, 256 tensor-memory columns:
+                             // two CTAs per SM cover each other's start, end and softmax phases
 };
 
 // KIND, D, BLOCK_N, STAGES are compile-time tuning keys (BLOCK_N: KV tile of the single-role kernel, 128
@@ -50,6 +53,8 @@ inline void flash_attn_sm100(const operand_t* q, const operand_t* k, const opera
     rc = sm100::launch_attn_fwd_ws<D, BLOCK_N, STAGES>(q, k, v, o, shp, st, ex, causal, scale, stream);
   } else if constexpr (KIND == kAttnAlternating) {
     rc = sm100::launch_attn_fwd_alt<D, STAGES, 1>(q, k, v, o, shp, st, ex, causal, scale, stream);
+  } else if constexpr (KIND == kAttnOneTile) {
+    rc = sm100::launch_attn_fwd_one<D, BLOCK_N, STAGES>(q, k, v, o, shp, st, ex, causal, scale, stream);
   } else {
     static_assert(KIND == kAttnPaired, "unknown kernel kind");
     static_assert(D == 128, "the paired kernel is built for head dim 128");

@@ -80,20 +80,20 @@ static constexpr float kRescaleThreshold = 8.0f;
 
 // t_s        tensor-memory address of this thread's lane at column 0 of the S tile (P overwrites it)
 // p_bar      PCHUNKS consecutive mbarriers, arrival count 4 (one per warp of the group): chunk q of P stored
-// corr_bar   mbarrier (count 4) telling the correction group that alpha_slot holds this step's factor
-// alpha_slot where this row's rescale factor is published (skipped on the first tile of a row)
-// first_tile no running state yet: the tile max becomes the offset, nothing is published
+// rescale_o  called by every thread with the factor its row of O has to be multiplied by before this
+//            step's P.V (1 when the offset stays; not called on the first tile of a row): the two-tile
+//            kernel publishes it to its correction group, the one-tile kernel rescales O on the spot
+// first_tile no running state yet: the tile max becomes the offset
 // MASK       some key of the tile is past seq_len or above the causal diagonal (two instantiations: the
 //            masking code costs the unmasked steps several per cent even when it is branched around)
 // The whole row is pulled into registers at once, the row max uses three-input max instructions, the
 // scaling and the row sum packed f32x2 arithmetic (one issue slot per pair).  Every exponential goes
 // to the special-function unit: a share by polynomial on the FMA pipe was measured slower here (the
 // chain softmax -> P.V -> next S bounds this kernel, not the unit).
-template <int BN, int PCHUNKS, bool MASK>
-__device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
-                                                bool first_tile, int kv0, int row, int seq_len, int causal,
-                                                float scale_log2, int lane, float& m_ref, float& l_run,
-                                                unsigned int* tr = nullptr) {
+template <int BN, int PCHUNKS, bool MASK, class Rescale>
+__device__ __forceinline__ void softmax_tile_with(uint32_t t_s, uint64_t* p_bar, Rescale&& rescale_o, bool first_tile, int kv0,
+                                                  int row, int seq_len, int causal, float scale_log2, int lane, float& m_ref,
+                                                  float& l_run, unsigned int* tr = nullptr) {
   static_assert(BN == 128, "written for 128-key tiles");
   static_assert(PCHUNKS == 4 || PCHUNKS == 2, "P is handed over in 4 chunks of 32 keys or 2 of 64");
   uint32_t sa[64], sb[64];
@@ -129,9 +129,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
       l_run *= alpha;
       m_ref = m_new;
     }
-    *alpha_slot = alpha;
-    __syncwarp();
-    if (lane == 0) mbar_arrive(corr_bar);
+    rescale_o(alpha);
   }
   FRAY_SM_TRACE(tr, 2);
   const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref * scale_log2;
@@ -208,6 +206,22 @@ __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint
   l_run += (r0 + r1) + (r2 + r3);
 }
 
+
+// The step with the factor handed to a correction group: alpha_slot receives this row's factor, corr_bar
+// (arrival count 4, one per warp) tells the group that the slots of this step are filled.
+template <int BN, int PCHUNKS, bool MASK>
+__device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
+                                             bool first_tile, int kv0, int row, int seq_len, int causal, float scale_log2,
+                                             int lane, float& m_ref, float& l_run, unsigned int* tr = nullptr) {
+  softmax_tile_with<BN, PCHUNKS, MASK>(
+      t_s, p_bar,
+      [&](float alpha) {
+        *alpha_slot = alpha;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(corr_bar);
+      },
+      first_tile, kv0, row, seq_len, causal, scale_log2, lane, m_ref, l_run, tr);
+}
 
 // Epilogue of one query tile, run by the 128 threads that own its rows (thread r = row r, reading its
 // own tensor-memory lane): O / l -> 16-bit -> shared memory (the tile's dead Q buffer, 128B-swizzled)
