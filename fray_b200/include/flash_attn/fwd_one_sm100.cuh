@@ -163,10 +163,10 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       };
       if (need_mask) {
-        softmax_tile_with<BN, Cfg::kPChunks, true>(t_s, p_full, rescale_o, j == 0, kv0, row, seq_k, causal, scale_log2, lane,
+        softmax_tile_with<BN, Cfg::kPChunks, true, false>(t_s, p_full, rescale_o, j == 0, kv0, row, seq_k, causal, scale_log2, lane,
                                                    m_ref, l_run);
       } else {
-        softmax_tile_with<BN, Cfg::kPChunks, false>(t_s, p_full, rescale_o, j == 0, kv0, row, seq_k, causal, scale_log2, lane,
+        softmax_tile_with<BN, Cfg::kPChunks, false, false>(t_s, p_full, rescale_o, j == 0, kv0, row, seq_k, causal, scale_log2, lane,
                                                     m_ref, l_run);
       }
     }

@@ -188,10 +188,10 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       unsigned int* tr = nullptr;
 #endif
       if (need_mask) {
-        softmax_tile<BN, Cfg::kPChunks, true>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, kv0, row, seq_k,
+        softmax_tile<BN, Cfg::kPChunks, true, D == 64>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, kv0, row, seq_k,
                                               causal, scale_log2, lane, m_ref, l_run, tr);
       } else {
-        softmax_tile<BN, Cfg::kPChunks, false>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, kv0, row, seq_k,
+        softmax_tile<BN, Cfg::kPChunks, false, D == 64>(t_s, p_bar, corr_ready + i, alpha_buf + i * 128 + r, j == 0, kv0, row, seq_k,
                                                causal, scale_log2, lane, m_ref, l_run, tr);
       }
       if (r == FRAY_TRACE_ROW) FRAY_TRACE(4, i, j);

@@ -84,18 +84,22 @@ static constexpr float kRescaleThreshold = 8.0f;
 //            step's P.V (1 when the offset stays; not called on the first tile of a row): the two-tile
 //            kernel publishes it to its correction group, the one-tile kernel rescales O on the spot
 // first_tile no running state yet: the tile max becomes the offset
+// SMALL_STORES  P is computed and stored in pieces of 32 keys (16 columns) instead of 64: fewer values live at a
+//            time; in the two-tile kernel measured +1 to +3.5 % at head dim 64 and -0.3 % at 128 (it chooses by
+//            head dim), in the one-tile kernel -1 to -2 % (it does not use it)
 // MASK       some key of the tile is past seq_len or above the causal diagonal (two instantiations: the
 //            masking code costs the unmasked steps several per cent even when it is branched around)
 // The whole row is pulled into registers at once, the row max uses three-input max instructions, the
 // scaling and the row sum packed f32x2 arithmetic (one issue slot per pair).  Every exponential goes
 // to the special-function unit: a share by polynomial on the FMA pipe was measured slower here (the
 // chain softmax -> P.V -> next S bounds this kernel, not the unit).
-template <int BN, int PCHUNKS, bool MASK, class Rescale>
+template <int BN, int PCHUNKS, bool MASK, bool SMALL_STORES, class Rescale>
 __device__ __forceinline__ void softmax_tile_with(uint32_t t_s, uint64_t* p_bar, Rescale&& rescale_o, bool first_tile, int kv0,
                                                   int row, int seq_len, int causal, float scale_log2, int lane, float& m_ref,
                                                   float& l_run, unsigned int* tr = nullptr) {
   static_assert(BN == 128, "written for 128-key tiles");
   static_assert(PCHUNKS == 4 || PCHUNKS == 2, "P is handed over in 4 chunks of 32 keys or 2 of 64");
+  static_assert(!SMALL_STORES || PCHUNKS == 2, "the 32-key pieces are written for two hand-over chunks");
   uint32_t sa[64], sb[64];
   tmem_ld_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sa[0]));
   tmem_ld_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sa[32]));
@@ -139,7 +143,8 @@ __device__ __forceinline__ void softmax_tile_with(uint32_t t_s, uint64_t* p_bar,
   // chunk q of P.  The hand-over of a chunk (wait for the store, fence, arrive) is issued after the NEXT
   // chunk's arithmetic: the store's latency then hides under that arithmetic, and only the last chunk's
   // wait sits in the step.
-  constexpr int KEYS = BN / PCHUNKS;
+  // keys per compute / store call: a hand-over chunk, or 32 with SMALL_STORES (two calls per chunk)
+  constexpr int KEYS = SMALL_STORES ? 32 : BN / PCHUNKS;
   auto compute = [&](const uint32_t (&h)[64], int off, uint32_t (&pk)[KEYS / 2]) {
 #pragma unroll
     for (int c = 0; c < KEYS; c += 8) {
@@ -175,7 +180,7 @@ __device__ __forceinline__ void softmax_tile_with(uint32_t t_s, uint64_t* p_bar,
     if (lane == 0) mbar_arrive(p_bar + q);
   };
   uint32_t pa[KEYS / 2], pb[KEYS / 2];
-  if constexpr (PCHUNKS == 4) {
+  if constexpr (PCHUNKS == 4 && !SMALL_STORES) {
     compute(sa, 0, pa);
     store(pa, 0);
     compute(sa, 32, pb);
@@ -188,6 +193,21 @@ __device__ __forceinline__ void softmax_tile_with(uint32_t t_s, uint64_t* p_bar,
     hand_over(2);
     store(pb, 3);
     hand_over(3);
+  } else if constexpr (SMALL_STORES) {
+    compute(sa, 0, pa);
+    store(pa, 0);
+    compute(sa, 32, pb);
+    store(pb, 1);
+    FRAY_SM_TRACE(tr, 3);
+    compute(sb, 0, pa);
+    FRAY_SM_TRACE(tr, 9);
+    hand_over(0);
+    FRAY_SM_TRACE(tr, 10);
+    store(pa, 2);
+    compute(sb, 32, pb);
+    store(pb, 3);
+    FRAY_SM_TRACE(tr, 11);
+    hand_over(1);
   } else {
     compute(sa, 0, pa);
     FRAY_SM_TRACE(tr, 3);
@@ -209,11 +229,11 @@ __device__ __forceinline__ void softmax_tile_with(uint32_t t_s, uint64_t* p_bar,
 
 // The step with the factor handed to a correction group: alpha_slot receives this row's factor, corr_bar
 // (arrival count 4, one per warp) tells the group that the slots of this step are filled.
-template <int BN, int PCHUNKS, bool MASK>
+template <int BN, int PCHUNKS, bool MASK, bool SMALL_STORES = false>
 __device__ __forceinline__ void softmax_tile(uint32_t t_s, uint64_t* p_bar, uint64_t* corr_bar, float* alpha_slot,
                                              bool first_tile, int kv0, int row, int seq_len, int causal, float scale_log2,
                                              int lane, float& m_ref, float& l_run, unsigned int* tr = nullptr) {
-  softmax_tile_with<BN, PCHUNKS, MASK>(
+  softmax_tile_with<BN, PCHUNKS, MASK, SMALL_STORES>(
       t_s, p_bar,
       [&](float alpha) {
         *alpha_slot = alpha;
