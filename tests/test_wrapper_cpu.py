@@ -145,3 +145,15 @@ def test_shard_units_partition(n, world):
         assert b == c and a <= b and c <= d
     sizes = [b - a for a, b in spans]
     assert max(sizes) - min(sizes) <= 1
+
+
+def test_timeline_tool_parses_without_a_gpu():
+    """The role-timeline tool imports nothing GPU-bound before it has parsed its arguments."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.run([sys.executable, "-m", "fray_b200.jit_kernels.timeline", "--help"], cwd=root,
+                          capture_output=True, text=True, timeout=120)
+    assert proc.returncode == 0, proc.stderr
+    assert "--warm" in proc.stdout and "--row" in proc.stdout
