@@ -9,6 +9,7 @@
 #include "fwd_ws_sm100.cuh"
 #include "fwd_alt_sm100.cuh"
 #include "fwd_one_sm100.cuh"
+#include "fwd_pers_sm100.cuh"
 
 namespace fray {
 
@@ -21,6 +22,8 @@ enum AttnKernelKind : int {
   kAttnPaired = 3,           // the same on a pair of CTAs (cta_group::2): 256 rows per pair, half of K and V per CTA
   kAttnOneTile = 4,          // one 128-row tile per CTA, producer / MMA / softmax roles, 256 tensor-memory columns:
                              // two CTAs per SM cover each other's start, end and softmax phases
+  kAttnPersistent = 5,       // kind 1 as one CTA per SM that walks through the work items, the next item's first
+                             // copies and scores behind the current item's last steps
 };
 
 // KIND, D, BLOCK_N, STAGES are compile-time tuning keys (BLOCK_N: KV tile of the single-role kernel, 128
@@ -55,6 +58,8 @@ inline void flash_attn_sm100(const operand_t* q, const operand_t* k, const opera
     rc = sm100::launch_attn_fwd_alt<D, STAGES, 1>(q, k, v, o, shp, st, ex, causal, scale, stream);
   } else if constexpr (KIND == kAttnOneTile) {
     rc = sm100::launch_attn_fwd_one<D, BLOCK_N, STAGES>(q, k, v, o, shp, st, ex, causal, scale, stream);
+  } else if constexpr (KIND == kAttnPersistent) {
+    rc = sm100::launch_attn_fwd_pers<D, BLOCK_N, STAGES>(q, k, v, o, shp, st, ex, causal, scale, stream);
   } else {
     static_assert(KIND == kAttnPaired, "unknown kernel kind");
     static_assert(D == 128, "the paired kernel is built for head dim 128");

@@ -175,6 +175,25 @@ inline int ensure_dynamic_smem(Kernel kernel, int bytes, int threads = 0, int re
   return kAttnOk;
 }
 
+// Number of SMs of the current device (cached per device of this process); 0 on failure.
+inline int device_sm_count() {
+  constexpr int kMaxDevices = 64;
+  static int count[kMaxDevices] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  if (dev >= 0 && dev < kMaxDevices && count[dev] > 0) return count[dev];
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  if (dev >= 0 && dev < kMaxDevices) count[dev] = n;
+  return n;
+}
+
 // Synchronising read of the sticky device status words; clears them when asked.
 inline int read_attn_status(int* out4, bool clear) {
   int host[4] = {0, 0, 0, 0};

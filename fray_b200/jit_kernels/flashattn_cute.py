@@ -75,7 +75,7 @@ _RC_TENSOR_MAP = 6
 
 
 # Kernel kinds (flash_attn/flash_attn_sm100.cuh).
-KIND_SIMPLE, KIND_TWO_TILES, KIND_ALTERNATING, KIND_PAIRED, KIND_ONE_TILE = 0, 1, 2, 3, 4
+KIND_SIMPLE, KIND_TWO_TILES, KIND_ALTERNATING, KIND_PAIRED, KIND_ONE_TILE, KIND_PERSISTENT = 0, 1, 2, 3, 4, 5
 
 
 def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
@@ -84,21 +84,24 @@ def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
 
     KIND: 0 single-role, 1 warp-specialised with two query tiles per CTA, 2 warp-specialised with one tile per CTA
     and two softmax groups on alternate KV steps, 3 the same on a pair of CTAs (2-CTA MMA; D = 128 only), 4
-    warp-specialised with one tile per CTA and two CTAs per SM (the kind for short sequences: a CTA's start and
-    end run beside its neighbour's steady state).
-    BLOCK_N: KV tile (64 or 128 for kind 0, 128 otherwise).  STAGES: K/V ring slots of kinds 1 and 4, K ring
+    warp-specialised with one tile per CTA and two CTAs per SM (a CTA's start and end run beside its neighbour's
+    steady state), 5 kind 1 as a persistent grid of one CTA per SM that walks through the work items (the next
+    item's first copies and scores sit behind the current item's last steps); 4 and 5 are the kinds for short
+    sequences.
+    BLOCK_N: KV tile (64 or 128 for kind 0, 128 otherwise).  STAGES: K/V ring slots of kinds 1, 4 and 5, K ring
     slots of kinds 2 and 3 (their V tiles use three slots).
     """
     space = [
         {"KIND": KIND_TWO_TILES, "BLOCK_N": 128, "STAGES": 4},
         {"KIND": KIND_TWO_TILES, "BLOCK_N": 128, "STAGES": 3},
+        {"KIND": KIND_PERSISTENT, "BLOCK_N": 128, "STAGES": 3},
         {"KIND": KIND_ONE_TILE, "BLOCK_N": 128, "STAGES": 2},
         {"KIND": KIND_ALTERNATING, "BLOCK_N": 128, "STAGES": 2 if d == 128 else 4},
         {"KIND": KIND_SIMPLE, "BLOCK_N": 128, "STAGES": 1},
         {"KIND": KIND_SIMPLE, "BLOCK_N": 64, "STAGES": 1},
     ]
     if d == 128:
-        space[3:3] = [{"KIND": KIND_PAIRED, "BLOCK_N": 128, "STAGES": 4}, {"KIND": KIND_PAIRED, "BLOCK_N": 128, "STAGES": 6}]
+        space[4:4] = [{"KIND": KIND_PAIRED, "BLOCK_N": 128, "STAGES": 4}, {"KIND": KIND_PAIRED, "BLOCK_N": 128, "STAGES": 6}]
     else:
         space.insert(1, {"KIND": KIND_TWO_TILES, "BLOCK_N": 128, "STAGES": 6})
     forced = _forced_point()
