@@ -57,7 +57,7 @@ int fray_attn_status(int* out4, int clear);
 
 /* out4 = {kernel kind (0 single-role, 1 two query tiles per CTA, 2 one tile per CTA with two softmax
  * groups on alternate KV steps, 3 the same on a CTA pair with 2-CTA MMA, 4 one tile per CTA with two
- * CTAs per SM), head dim D, KV tile length,
+ * CTAs per SM, 5 kind 1 as a persistent grid), head dim D, KV tile length,
  * K/V pipeline stages} this library was instantiated with - the template keys the reference keeps only in the source text
  * (fray/jit_kernels/flashattn_cute.py:32-38). */
 void fray_attn_kernel_info(int* out4);
