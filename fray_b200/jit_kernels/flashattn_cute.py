@@ -94,7 +94,7 @@ def tuning_space(d: int) -> Tuple[Dict[str, Any], ...]:
     space = [
         {"KIND": KIND_TWO_TILES, "BLOCK_N": 128, "STAGES": 4},
         {"KIND": KIND_TWO_TILES, "BLOCK_N": 128, "STAGES": 3},
-        {"KIND": KIND_PERSISTENT, "BLOCK_N": 128, "STAGES": 3},
+        {"KIND": KIND_PERSISTENT, "BLOCK_N": 128, "STAGES": 3 if d == 128 else 4},
         {"KIND": KIND_ONE_TILE, "BLOCK_N": 128, "STAGES": 2},
         {"KIND": KIND_ALTERNATING, "BLOCK_N": 128, "STAGES": 2 if d == 128 else 4},
         {"KIND": KIND_SIMPLE, "BLOCK_N": 128, "STAGES": 1},
