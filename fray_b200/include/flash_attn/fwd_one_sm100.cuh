@@ -67,7 +67,7 @@ template <int D, int BN, int STAGES>
 __global__ void __launch_bounds__(256, 2)
 attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, int num_heads,
-                    int seq_len, int causal, float scale_log2, int kv_group, float* lse, int seq_k) {
+                    int seq_len, int causal, float scale_log2, int kv_group, float* lse, int seq_k, int heaviest_first) {
   using Cfg = OneCfg<D, BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -87,9 +87,14 @@ attn_fwd_one_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int tile = causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;  // heaviest causal tiles first
+  // Grid order: (tiles, slices) runs slice by slice, so that CTAs side by side share a slice's K and V in
+  // L2; with heaviest_first the axes are swapped and all slices' longest causal tiles start first, which
+  // balances a causal problem of few rounds of CTAs (the launcher decides, see heaviest_first_order).
+  const int n_x = heaviest_first ? gridDim.y : gridDim.x;
+  const int px = heaviest_first ? blockIdx.y : blockIdx.x;
+  const int tile = causal ? (n_x - 1 - px) : px;  // heaviest causal tiles first
   const int m0 = tile * Cfg::BM;
-  const int bh = blockIdx.y;
+  const int bh = heaviest_first ? blockIdx.x : blockIdx.y;
   const int b = bh / num_heads;
   const int h = bh - b * num_heads;
   const int h_kv = h / kv_group;
@@ -283,9 +288,12 @@ inline int launch_attn_fwd_one(const operand_t* q, const operand_t* k, const ope
   auto kernel = attn_fwd_one_kernel<D, BN, STAGES>;
   rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes, Cfg::kThreads, 128 * Cfg::kRegsSoftmax + 128 * Cfg::kRegsOther);
   if (rc != kAttnOk) return rc;
-  dim3 grid((shp.S + Cfg::BM - 1) / Cfg::BM, shp.B * shp.H);
+  const int heaviest_first = heaviest_first_order(causal, shp, shp_kv) ? 1 : 0;
+  const unsigned n_x = (shp.S + Cfg::BM - 1) / (Cfg::BM), n_bh = shp.B * shp.H;
+  dim3 grid(heaviest_first ? n_bh : n_x, heaviest_first ? n_x : n_bh);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,
-                                                           scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k);
+                                                           scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k,
+                                                           heaviest_first);
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
   return kAttnOk;
 }

@@ -484,10 +484,8 @@ inline int launch_attn_fwd_pers(const operand_t* q, const operand_t* k, const op
   if (sms <= 0) return kAttnLaunchFailed;
   const long long items = static_cast<long long>((shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM)) * shp.B * shp.H;
   const int grid = static_cast<int>(items < sms ? items : sms);
-  // item order (see the kernel): heaviest first over all slices when the mask makes the items unequal and
-  // all of K and V fit L2 comfortably, slice by slice otherwise
-  const long long kv_bytes = 2LL * shp_kv.B * shp_kv.H * shp_kv.S * shp_kv.D * 2;
-  const int blk = (causal && kv_bytes <= 48LL * 1000 * 1000) ? shp.B * shp.H : 1;
+  // item order (see the kernel): heaviest first over all slices or slice by slice
+  const int blk = heaviest_first_order(causal, shp, shp_kv) ? shp.B * shp.H : 1;
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.B * shp.H, shp.S, causal ? 1 : 0,
                                                            scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k, blk);
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;

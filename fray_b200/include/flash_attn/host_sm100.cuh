@@ -175,6 +175,19 @@ inline int ensure_dynamic_smem(Kernel kernel, int bytes, int threads = 0, int re
   return kAttnOk;
 }
 
+// Order in which the query tiles of a causal problem start: slice by slice (CTAs side by side share a slice's
+// K and V in L2), or the heaviest tiles of ALL (batch, head) slices first, which lets the hardware's
+// first-come scheduling even out the tiles' unequal lengths.  Measured on 4096- and 16384-row causal problems,
+// heaviest first gains 7-45 % while there are at most seven rounds of CTAs (K and V up to 134 MB) and is level
+// or slightly behind at fourteen rounds (256 MB: K and V of the slices in flight no longer share L2); at 1024
+// and 2048 rows, where a slice's few tiles run side by side anyway, it loses up to 13 %.
+static constexpr long long kHeaviestFirstMaxKvBytes = 160LL * 1000 * 1000;
+static constexpr int kHeaviestFirstMinRows = 4096;
+inline bool heaviest_first_order(bool causal, const AttnShape& shp, const AttnShape& shp_kv) {
+  const long long kv_bytes = 2LL * shp_kv.B * shp_kv.H * shp_kv.S * shp_kv.D * 2;
+  return causal && shp.S >= kHeaviestFirstMinRows && kv_bytes <= kHeaviestFirstMaxKvBytes;
+}
+
 // Number of SMs of the current device (cached per device of this process); 0 on failure.
 inline int device_sm_count() {
   constexpr int kMaxDevices = 64;
