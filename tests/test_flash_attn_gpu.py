@@ -192,6 +192,20 @@ def test_causal_first_row_copies_v0_and_last_row_sees_everything(variant):
     assert (out[0, 0, -1].float() - full[0, 0, -1].float()).abs().max() <= 2e-3
 
 
+def test_causal_heaviest_tiles_first_order(variant):
+    """A causal problem of 4096 rows whose K and V are small: the launchers of the two-tile, one-tile and
+    persistent kernels then start the heaviest tiles of all (batch, head) slices first (swapped grid axes, or
+    the persistent kernel's block order); every row of every slice must still land where it belongs."""
+    g = torch.Generator().manual_seed(17)
+    q, k, v = (torch.randn(1, 3, 4096, 64, generator=g).half().cuda() for _ in range(3))
+    out = run_op(q, k, v, causal=True)
+    check(out, q, k, v, causal=True)
+    # 5 slices, ragged length: the last pair of every slice has one tile only
+    q, k, v = (torch.randn(1, 5, 4200, 128, generator=g).half().cuda() for _ in range(3))
+    out = run_op(q, k, v, causal=True)
+    check(out, q, k, v, causal=True)
+
+
 def test_noncontiguous_output_receives_result(variant):
     g = torch.Generator().manual_seed(9)
     q, k, v = (torch.randn(2, 4, 256, 64, generator=g).half().cuda() for _ in range(3))
