@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(512, 1)
 attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                    int num_heads, int seq_len, int causal, float scale_log2, int kv_group, float* lse, int seq_k,
-                   int heaviest_first) {
+                   int group_slices, int num_bh) {
   using Cfg = WsCfg<D, BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -111,14 +111,18 @@ attn_fwd_ws_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  // Grid order: (tiles, slices) runs slice by slice, so that CTAs side by side share a slice's K and V in
-  // L2; with heaviest_first the axes are swapped and all slices' longest causal tiles start first, which
-  // balances a causal problem of few rounds of CTAs (the launcher decides, see heaviest_first_order).
-  const int n_x = heaviest_first ? gridDim.y : gridDim.x;
-  const int px = heaviest_first ? blockIdx.y : blockIdx.x;
+  // Grid order.  group_slices == 0: (tiles, slices), which runs slice by slice, so that CTAs side by side share
+  // a slice's K and V in L2.  group_slices > 0: (slice inside its group, tiles, groups): the longest causal
+  // tiles of all slices of a group start first, which lets first-come scheduling even out the tiles' unequal
+  // lengths, while a group's K and V stay small enough to share L2 (the launcher decides, see
+  // heaviest_first_group).
+  const int n_x = group_slices > 0 ? gridDim.y : gridDim.x;
+  const int px = group_slices > 0 ? blockIdx.y : blockIdx.x;
   const int pair = causal ? (n_x - 1 - px) : px;  // heaviest causal tiles first
+  const int bh = group_slices > 0 ? static_cast<int>(blockIdx.z) * group_slices + static_cast<int>(blockIdx.x)
+                                  : static_cast<int>(blockIdx.y);
+  if (bh >= num_bh) return;  // padding of the last group
   const int m0 = pair * (2 * Cfg::BM);
-  const int bh = heaviest_first ? blockIdx.x : blockIdx.y;
   const int b = bh / num_heads;
   const int h = bh - b * num_heads;
   const int h_kv = h / kv_group;  // K/V head of this query head (one division per CTA, not per copy)
@@ -394,12 +398,12 @@ inline int launch_attn_fwd_ws(const operand_t* q, const operand_t* k, const oper
   auto kernel = attn_fwd_ws_kernel<D, BN, STAGES>;
   rc = ensure_dynamic_smem<Cfg>(kernel, Cfg::kSmemBytes, Cfg::kThreads, 256 * Cfg::kRegsSoftmax + 128 * Cfg::kRegsCorrection + 128 * Cfg::kRegsOther);
   if (rc != kAttnOk) return rc;
-  const int heaviest_first = heaviest_first_order(causal, shp, shp_kv) ? 1 : 0;
+  const int group_slices = heaviest_first_group(causal, shp, shp_kv);
   const unsigned n_x = (shp.S + 2 * Cfg::BM - 1) / (2 * Cfg::BM), n_bh = shp.B * shp.H;
-  dim3 grid(heaviest_first ? n_bh : n_x, heaviest_first ? n_x : n_bh);
+  dim3 grid = group_slices > 0 ? dim3(group_slices, n_x, (n_bh + group_slices - 1) / group_slices) : dim3(n_x, n_bh);
   kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, shp.H, shp.S, causal ? 1 : 0,
                                                            scale * 1.44269504088896340736f, ex.kv_group, ex.lse, ex.seq_k,
-                                                           heaviest_first);
+                                                           group_slices, static_cast<int>(n_bh));
   if (cudaGetLastError() != cudaSuccess) return kAttnLaunchFailed;
   return kAttnOk;
 }

@@ -183,9 +183,16 @@ inline int ensure_dynamic_smem(Kernel kernel, int bytes, int threads = 0, int re
 // and 2048 rows, where a slice's few tiles run side by side anyway, it loses up to 13 %.
 static constexpr long long kHeaviestFirstMaxKvBytes = 160LL * 1000 * 1000;
 static constexpr int kHeaviestFirstMinRows = 4096;
+// The same decision as a group size for kernels whose grid is (slice inside its group, tiles, groups): all
+// slices in one group, or 0 for slice by slice.  (Several groups of slices that each stay under the limit were
+// measured on the 256 MB configurations: no difference from slice by slice within the run-to-run spread.)
+inline int heaviest_first_group(bool causal, const AttnShape& shp, const AttnShape& shp_kv);
 inline bool heaviest_first_order(bool causal, const AttnShape& shp, const AttnShape& shp_kv) {
   const long long kv_bytes = 2LL * shp_kv.B * shp_kv.H * shp_kv.S * shp_kv.D * 2;
   return causal && shp.S >= kHeaviestFirstMinRows && kv_bytes <= kHeaviestFirstMaxKvBytes;
+}
+inline int heaviest_first_group(bool causal, const AttnShape& shp, const AttnShape& shp_kv) {
+  return heaviest_first_order(causal, shp, shp_kv) ? shp.B * shp.H : 0;
 }
 
 // Number of SMs of the current device (cached per device of this process); 0 on failure.
