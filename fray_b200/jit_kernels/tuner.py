@@ -63,13 +63,14 @@ class JITTuner:
         """Milliseconds for ``launches`` back-to-back calls after an L2 flush (reference: tuner.py:52-63).
 
         Differences from the reference: three untimed launches first (the first launch of a library pays
-        module loading and the tensor-map encodings), and the better of two timed rounds, so that a
-        candidate is not dropped for one slow round on a shared machine.
+        module loading and the tensor-map encodings), and the best of three timed rounds, so that a
+        candidate is not dropped for one slow round (causal shapes were seen to vary by 10 % from run to
+        run on one box).
         """
         for _ in range(3):
             assert runtime(*args) == 0
         best = None
-        for _ in range(2):
+        for _ in range(3):
             start = torch.cuda.Event(enable_timing=True)
             end = torch.cuda.Event(enable_timing=True)
             torch.empty(int(256e6 // 4), dtype=torch.int, device="cuda").zero_()
